@@ -29,7 +29,7 @@ extern "C" {
 
 #define SLLM_ABI_VERSION 1
 
-typedef enum { SLLM_F16 = 0, SLLM_BF16 = 1 } sllm_dtype_t;
+typedef enum { SLLM_F16 = 0, SLLM_BF16 = 1, SLLM_F32 = 2 } sllm_dtype_t; /* F32: only where a function says so */
 typedef void* sllm_stream_t; /* cudaStream_t */
 
 /* ---- library ---- */
@@ -214,6 +214,42 @@ int sllm_swap_blocks(const int64_t* host_src_ids, const int64_t* host_dst_ids, i
 int sllm_swap_blocks_gathered(const int64_t* src_ids, const int64_t* dst_ids, int64_t n, int is_swap_in, void* k_cache,
                               void* v_cache, void* host_k_swap, void* host_v_swap, int64_t block_bytes,
                               sllm_stream_t stream);
+
+/* ---- Parallel decoder blocks with an fp32 residual stream (new; the reference has no such model).  `dtype` is the storage
+ * type of projections / activations and may be SLLM_F32; sums and norms are computed in fp32 for every dtype.
+ * add_rmsnorm_f32: residual (fp32 [T, width]) += a + b (dtype, [T, width], either may be NULL), then
+ * out = residual / sqrt(mean(residual^2) + eps) * weight (dtype). */
+int sllm_add_rmsnorm_f32(void* residual, const void* a, const void* b, const void* weight, void* out, float eps,
+                         int64_t num_tokens, int width, sllm_dtype_t dtype, sllm_stream_t stream);
+/* RMS norm of the first n columns of row-strided matrices (a slice of a fused projection): out = x / rms(x) * weight. */
+int sllm_rmsnorm_strided(const void* x, int64_t x_row_stride, const void* weight, void* out, int64_t out_row_stride,
+                         float eps, int64_t num_tokens, int n, sllm_dtype_t dtype, sllm_stream_t stream);
+/* x = relu(x)^2 over n contiguous elements. */
+int sllm_relu2_inplace(void* x, int64_t n, sllm_dtype_t dtype, sllm_stream_t stream);
+/* Mixture-of-experts router: logits fp32 [T, experts] -> weights fp32 [T, experts] = softmax over the `top` largest logits of
+ * each row at their positions, 0 elsewhere.  top <= 32, experts <= 2048. */
+int sllm_moe_route(const void* logits, void* weights, int64_t num_tokens, int experts, int top, sllm_stream_t stream);
+/* u [T, experts * ff] (dtype) = relu(u)^2 * weights[t, column / ff]: experts a token does not use contribute exact zeros. */
+int sllm_moe_relu2_scale_inplace(void* u, const void* weights, int64_t num_tokens, int experts, int ff, sllm_dtype_t dtype,
+                                 sllm_stream_t stream);
+
+/* ---- Latent attention over a paged cache of per-token rows [c (r) | k_rot (dr)] shared by all heads (new).
+ * cache: [num_blocks, n_slots, block_size, r + dr] (dtype); tok_seq / tok_pos: int32 [T], the block-table row and the position
+ * of every token of the step; cos / sin: fp32 [T, rot_dims / 2], the rotary angles of the tokens' positions (pairs (2i, 2i+1)).
+ * latent_kv_store: c = rmsnorm(dkv[:, :r]) * norm_weight, k_rot = rotary(dkv[:, r : r + dr]) -> the tokens' cache rows. */
+int sllm_latent_kv_store(const void* dkv, int64_t row_stride, const void* norm_weight, const void* cosb, const void* sinb,
+                         const void* tok_seq, const void* tok_pos, const void* block_table, int max_blocks_per_seq,
+                         void* cache, int n_slots, int slot, int block_size, int64_t num_tokens, int r, int dr, int rot_dims,
+                         float eps, sllm_dtype_t dtype, sllm_stream_t stream);
+/* latent_attention: per token i at position p and head h, over the cached positions max(0, p - window + 1) .. p (all of 0 .. p
+ * when window <= 0): out[i, h, :r] = sigmoid(gate[i, h]) * sum_j softmax_j((q_lat[i,h] . c_j + rotary(q_rot[i,h]) . k_rot_j) * scale) c_j.
+ * q_lat / q_rot / out: element strides per token and per head; gate: [T, num_heads] logits (row stride) or NULL.  r <= 512. */
+int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_lat_stride_h, const void* q_rot,
+                          int64_t q_rot_stride_t, int64_t q_rot_stride_h, const void* cosb, const void* sinb,
+                          const void* gate, int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
+                          const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos,
+                          void* out, int64_t out_stride_t, int64_t out_stride_h, int64_t num_tokens, int num_heads, int r,
+                          int dr, int rot_dims, int window, float scale, sllm_dtype_t dtype, sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

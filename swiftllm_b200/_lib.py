@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # SLLM_LIB_PATH: a development variant of the library (python -m swiftllm_b200.build with SLLM_BUILD_VARIANT); never set by tests / bench
 LIB_PATH = os.environ.get("SLLM_LIB_PATH") or os.path.join(_HERE, "libswiftllm_b200.so")
 
-F16, BF16 = 0, 1
+F16, BF16, F32 = 0, 1, 2
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 
@@ -43,6 +43,14 @@ SIGNATURES = {
     "sllm_allreduce_add_rmsnorm_ll": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _F, _L, _I, _L, _I, _P]),
     "sllm_swap_blocks": (_I, [_P, _P, _L, _I, _P, _P, _P, _P, _L, _P]),
     "sllm_swap_blocks_gathered": (_I, [_P, _P, _L, _I, _P, _P, _P, _P, _L, _P]),
+    "sllm_add_rmsnorm_f32": (_I, [_P, _P, _P, _P, _P, _F, _L, _I, _I, _P]),
+    "sllm_rmsnorm_strided": (_I, [_P, _L, _P, _P, _L, _F, _L, _I, _I, _P]),
+    "sllm_relu2_inplace": (_I, [_P, _L, _I, _P]),
+    "sllm_moe_route": (_I, [_P, _P, _L, _I, _I, _P]),
+    "sllm_moe_relu2_scale_inplace": (_I, [_P, _P, _L, _I, _I, _I, _P]),
+    "sllm_latent_kv_store": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _F, _I, _P]),
+    "sllm_latent_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I,
+                                   _I, _I, _I, _F, _I, _P]),
 }
 
 _lib = None
@@ -99,6 +107,11 @@ def dtype_tag(dtype: torch.dtype) -> int:
     if dtype == torch.bfloat16:
         return BF16
     raise TypeError(f"swiftllm_b200 kernels support float16 and bfloat16, got {dtype}")
+
+
+def dtype_tag_f32(dtype: torch.dtype) -> int:
+    """Tag for the kernels that are also instantiated for float storage (fp32 residual-stream models)."""
+    return F32 if dtype == torch.float32 else dtype_tag(dtype)
 
 
 def stream() -> int:

@@ -22,7 +22,7 @@ class EngineConfig:
     max_tokens_in_batch: int
 
     # ---- additions ----
-    dtype: str = "float16"          # "float16" (the reference's hard-coded dtype) or "bfloat16"
+    dtype: str = "float16"          # "float16" (the reference's hard-coded dtype), "bfloat16", or "float32" (workers with fp32 kernels)
     tp_size: int = 1                # tensor-parallel world size (heads / FFN columns), one process per GPU
     tp_rank: int = 0
     pin_swap_space: bool = True     # the reference's swap space is pageable (model.py:158-159)
@@ -67,5 +67,5 @@ class EngineConfig:
         parser.add_argument("--max-blocks-per-seq", type=int, default=32768, help="Maximum number of blocks per sequence")
         parser.add_argument("--max-batch-size", type=int, default=512, help="Maximum batch size")
         parser.add_argument("--max-tokens-in-batch", type=int, default=32768, help="Maximum number of tokens in a batch")
-        parser.add_argument("--dtype", type=str, default="float16", choices=["float16", "bfloat16"])
+        parser.add_argument("--dtype", type=str, default="float16", choices=["float16", "bfloat16", "float32"])
         parser.add_argument("--use-cuda-graph", action="store_true")

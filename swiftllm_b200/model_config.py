@@ -3,8 +3,10 @@
 The attribute names are the ones the reference's worker reads (`swiftllm/model_config.py:5-46`): num_layers, num_q_heads,
 num_kv_heads, hidden_size, head_dim, vocab_size, max_position_embeddings, ffn_inter_dim, rotary_base / rope_theta,
 rms_norm_eps, rope_scaling (1.0 when absent or null; a dict for Llama 3.2 style scaling) and get_kvslot_size()."""
+import dataclasses
 import json
 import os
+from typing import Optional
 
 import torch
 
@@ -21,6 +23,8 @@ _REQUIRED = {
 
 
 class LlamaModelConfig:
+    family = "llama"
+
     def __init__(self, model_config: dict):
         arch, act = model_config.get("model_type"), model_config.get("hidden_act")
         assert arch == "llama", f"only the llama architecture is served, got model_type={arch!r}"
@@ -57,3 +61,93 @@ LLAMA3_8B = dict(model_type="llama", num_hidden_layers=32, num_attention_heads=3
 LLAMA3_70B = dict(model_type="llama", num_hidden_layers=80, num_attention_heads=64, num_key_value_heads=8,
                   hidden_size=8192, intermediate_size=28672, vocab_size=128256, max_position_embeddings=8192,
                   rope_theta=500000.0, rms_norm_eps=1e-5, hidden_act="silu", rope_scaling=None)
+
+
+# ---------------------------------------------------------------- Bupozen
+@dataclasses.dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Sizes and constants of one latent-attention mixer.  Per head: `dim` un-rotated and `rot_dim` rotated query / key entries,
+    `vdim` value entries; all heads share one key/value latent of `kv_rank` entries plus one rotated key part of `rot_dim`."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    window: int                 # a query at position p sees p - window + 1 .. p; 0 = everything up to p
+    rot_base: float
+    rot_dims: int               # leading entries of the rotated part that turn (interleaved pairs); the rest pass through
+    scale: float
+    kv_from: Optional[int]      # layer whose cached latent / rotated key part this layer reads instead of making its own
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_rank + self.rot_dim
+
+
+@dataclasses.dataclass(frozen=True)
+class FeedForwardSpec:
+    kind: str                   # "dense" | "moe"
+    ff: int                     # hidden size of the dense layer / of ONE expert
+    experts: int = 0
+    top: int = 0
+
+
+class BupozenModelConfig:
+    """config.json of the Bupozen design: {"architecture": "Bupozen", "vocab", "width", "norm": {"eps"}, "layers": [{"type",
+    "mixer": {...}, "mlp": {...} | null}, ...]}.  Every layer is a parallel block (one RMS norm feeds the mixer and the
+    feed-forward); every size may differ from layer to layer."""
+    family = "bupozen"
+
+    def __init__(self, model_config: dict):
+        assert model_config.get("architecture") == "Bupozen", f"not a Bupozen config: {model_config.get('architecture')!r}"
+        self.raw = dict(model_config)
+        self.vocab_size = int(model_config["vocab"])
+        self.hidden_size = int(model_config["width"])
+        self.rms_norm_eps = float(model_config["norm"]["eps"])
+        self.mixers, self.ffs = [], []
+        for i, layer in enumerate(model_config["layers"]):
+            assert layer["type"] == "latent_attention", f"layer {i}: unknown mixer type {layer['type']!r}"
+            m = layer["mixer"]
+            rot = m.get("rot") or {}
+            mask = m.get("mask") or {}
+            spec = LatentAttentionSpec(
+                heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]),
+                q_rank=int(m["q_rank"]), window=int(mask.get("size", 0)), rot_base=float(rot.get("base", 10000.0)),
+                rot_dims=int(rot.get("dims", m["rot_dim"])), scale=float(m["scale"]),
+                kv_from=None if m.get("kv_from") is None else int(m["kv_from"]))
+            assert spec.rot_dims % 2 == 0 and spec.rot_dims <= spec.rot_dim, f"layer {i}: rot.dims must be even and <= rot_dim"
+            if spec.kv_from is not None:
+                src = self.mixers[spec.kv_from] if spec.kv_from < i else None
+                assert src is not None and src.kv_from is None and src.cache_width == spec.cache_width and \
+                    src.kv_rank == spec.kv_rank, f"layer {i}: kv_from must name an earlier layer with its own latent of the same sizes"
+            self.mixers.append(spec)
+            f = layer.get("mlp")
+            if f is None:
+                self.ffs.append(None)
+            elif f["kind"] == "dense":
+                self.ffs.append(FeedForwardSpec("dense", int(f["ff"])))
+            else:
+                assert f["kind"] == "moe", f"layer {i}: unknown mlp kind {f['kind']!r}"
+                self.ffs.append(FeedForwardSpec("moe", int(f["expert"]["ff"]), int(f["router"]["experts"]), int(f["router"]["top"])))
+        self.num_layers = len(self.mixers)
+        # cache geometry: layers that make their own latent own a slot; slots are grouped by row width (one tensor per width)
+        self.cache_slot = {}            # layer -> (row width, slot within that width's tensor)
+        self.cache_slots_per_width = {}
+        for i, s in enumerate(self.mixers):
+            if s.kv_from is None:
+                n = self.cache_slots_per_width.get(s.cache_width, 0)
+                self.cache_slot[i] = (s.cache_width, n)
+                self.cache_slots_per_width[s.cache_width] = n + 1
+        for i, s in enumerate(self.mixers):
+            if s.kv_from is not None:
+                self.cache_slot[i] = self.cache_slot[s.kv_from]
+
+    def get_kvslot_size(self, dtype: torch.dtype = torch.bfloat16) -> int:
+        """Bytes of cache one token occupies: one [latent | rotated key part] row per layer that makes its own."""
+        return sum(w * n for w, n in self.cache_slots_per_width.items()) * dtype.itemsize
+
+    @staticmethod
+    def load_from_model_path(model_path: str) -> "BupozenModelConfig":
+        with open(os.path.join(model_path, "config.json"), "r", encoding="utf-8") as f:
+            return BupozenModelConfig(json.load(f))

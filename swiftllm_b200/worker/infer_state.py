@@ -49,3 +49,22 @@ class LlamaInferState:
     # the KV cache.  None = whole prompts, attention over the packed k/v.
     prefill_prefix_lens: Optional[torch.Tensor] = None  # [num_prefill_seqs]
     max_prefill_kv_len: int = 0                          # max_i(prefix_i + chunk_i); 0 when not chunked
+
+
+@dataclasses.dataclass
+class TokenInferState:
+    """Per-forward metadata of workers whose attention treats every token of the step as a query with its own (sequence,
+    position) - prompt portions and decoded tokens alike.  Batch layout as above: prompt portions first, then one row per
+    decoding sequence.  All tensors int32 on the model's device."""
+    batch_size: int
+    num_tokens: int
+    seq_ids: torch.Tensor                           # [batch_size] block-table row of every sequence
+    num_prefill_seqs: int
+    num_decoding_seqs: int
+    num_prefill_tokens: int
+    token_seq_ids: torch.Tensor                     # [num_tokens] block-table row of every token
+    token_positions: torch.Tensor                   # [num_tokens] position of every token within its sequence
+    output_rows: torch.Tensor                       # rows whose logits are computed: the last row of every sequence, then extras
+    ignore_kvcache: bool = False                    # memory-profiling forward: no cache store, no attention
+    # rotary angle tables of the step, keyed by (base, dims): (cos, sin) fp32 [num_tokens, dims / 2]
+    rotary: dict = dataclasses.field(default_factory=dict)

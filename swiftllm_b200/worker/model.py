@@ -30,6 +30,7 @@ from swiftllm_b200.worker.block_manager import BlockManager
 from swiftllm_b200.worker.weight import load_weights
 
 from .infer_state import LlamaInferState
+from .model_base import PagedModelBase
 from .layers.post_layer import LlamaPostLayer
 from .layers.pre_layer import LlamaPreLayer
 from .layers.transformer_layer import LlamaTransformerLayer
@@ -73,7 +74,7 @@ def build_rope_tables(model_config: LlamaModelConfig, dtype: torch.dtype):
     return torch.cos(freqs).to(dtype), torch.sin(freqs).to(dtype)
 
 
-class LlamaModel:
+class LlamaModel(PagedModelBase):
     @torch.inference_mode()
     def __init__(self, engine_config: EngineConfig, model_config: Optional[LlamaModelConfig] = None):
         """`model_config` may be given directly (synthetic-weight runs); otherwise it is read from
@@ -100,12 +101,8 @@ class LlamaModel:
         self.cpu_block_manager = self.gpu_block_manager = None
         self.tp_group = None
         self._graphs = {}
-        # pinned staging ring for per-step metadata (eager path): a slot is rewritten only after the H2D copy that last read it
-        # has completed (event per slot), so back-to-back forward_async calls never race the copy engine
-        self._stage_ring = []
-        self._stage_next = 0
-        self._swap_stream = None        # EngineConfig.swap_on_copy_stream: dedicated copy stream + "copies done" event
-        self._swap_done = None
+        self._init_staging()
+        self._swap_stream = None        # EngineConfig.swap_on_copy_stream: dedicated copy stream (its "done" event: base class)
 
     # ------------------------------------------------------------------ init
     @torch.inference_mode()
@@ -251,44 +248,6 @@ class LlamaModel:
             return self.post_layer.forward(normed, infer_state, already_normed=True)
         input_embds += residual_buf
         return self.post_layer.forward(input_embds, infer_state)
-
-    _STAGE_SLOTS = 4
-
-    def _stage_slot(self, n: int):
-        """Next slot of the persistent pinned ring, grown geometrically; waits (host side) for the copy that last used it."""
-        i = self._stage_next
-        self._stage_next = (i + 1) % self._STAGE_SLOTS
-        if len(self._stage_ring) <= i:
-            self._stage_ring.append(None)
-        slot = self._stage_ring[i]
-        if slot is None or slot[0].numel() < n:
-            cap = max(4096, 1 << (max(n, 1) - 1).bit_length())
-            if slot is not None:
-                slot[1].synchronize()
-            slot = (torch.empty((cap,), dtype=torch.int32).pin_memory(), torch.cuda.Event())
-            self._stage_ring[i] = slot
-        else:
-            slot[1].synchronize()                # no-op unless the copy engine is more than _STAGE_SLOTS steps behind
-        return slot
-
-    def _wait_for_swaps(self):
-        """Device-side wait (no host sync) for swap copies enqueued on the copy stream since the last forward."""
-        if self._swap_done is not None and not (torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()):
-            torch.cuda.current_stream().wait_event(self._swap_done)
-            self._swap_done = None
-
-    def _stage_metadata(self, *parts):
-        """One persistent pinned host buffer (ring of slots), one async H2D copy; returns int32 device views (one per list)."""
-        flat = np.fromiter(itertools.chain(*parts), dtype=np.int32)
-        host, ev = self._stage_slot(flat.size)
-        host[:flat.size].numpy()[:] = flat
-        dev = host[:flat.size].to(self.device, non_blocking=True)
-        ev.record()
-        views, off = [], 0
-        for p in parts:
-            views.append(dev[off:off + len(p)])
-            off += len(p)
-        return views
 
     @torch.inference_mode()
     def forward(self, input_ids_list: list, seq_ids_list: list, decoding_seq_lens_list: list,
@@ -513,10 +472,3 @@ class LlamaModel:
     def swap_out_seqs(self, seq_ids_list: list):
         """Move the blocks of the given sequences from the GPU cache to the CPU swap space."""
         self._swap(seq_ids_list, False)
-
-    @torch.inference_mode()
-    def free_seqs_resources(self, seq_ids_list: list):
-        """model.py:401-408."""
-        seq_ids = torch.tensor(seq_ids_list, dtype=torch.int32, device=self.device)
-        self.gpu_block_manager.free_blocks_for_seqs(seq_ids, seq_ids_list=seq_ids_list)
-        self.cpu_block_manager.free_blocks_for_seqs(seq_ids, seq_ids_list=seq_ids_list)

@@ -95,6 +95,70 @@ class LlamaWeight:
             layer.load_weights(getter, tp_rank, tp_size, device)
 
 
+class BupozenLayerWeight:
+    """One parallel block.  Checkpoint names: `l<i>.norm1`, `l<i>.mix.{dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o}` (no dkv*
+    in a layer that reads another layer's cache), `l<i>.mlp.{up, down}` or `l<i>.mlp.{router, e<k>.up, e<k>.down}`.
+    Fusions made at load time: every projection that reads the block's normed input and feeds fp32 post-processing is one GEMM
+    operand (`in_proj` = [dq ; g ; dkv]); the experts are concatenated (`up` rows / `down` columns expert by expert)."""
+
+    def __init__(self, layer_id: int, model_config, dtype: torch.dtype):
+        self.layer_id, self.model_config, self.dtype = layer_id, model_config, dtype
+
+    def load_weights(self, getter: Callable, device):
+        c, i = self.model_config, self.layer_id
+        m, f, W = c.mixers[i], c.ffs[i], c.hidden_size
+
+        def get(name, shape, dtype=None):
+            w = getter(f"l{i}.{name}", shape, dtype or self.dtype)
+            assert isinstance(w, torch.Tensor) and tuple(w.shape) == tuple(shape), f"l{i}.{name}: expected shape {tuple(shape)}"
+            return w.to(device=device, dtype=dtype or self.dtype).contiguous()
+
+        self.norm = get("norm1", (W,))
+        parts = [get("mix.dq", (m.q_rank, W)), get("mix.g", (m.heads, W))]
+        if m.kv_from is None:
+            parts.append(get("mix.dkv", (m.cache_width, W)))
+            self.dkv_norm = get("mix.dkv.norm", (m.kv_rank,))
+        self.in_proj = torch.cat(parts, dim=0).contiguous()
+        self.dq_norm = get("mix.dq.norm", (m.q_rank,))
+        self.uq = get("mix.uq", (m.heads * (m.dim + m.rot_dim), m.q_rank))
+        self.uk = get("mix.uk", (m.heads * m.dim, m.kv_rank)).view(m.heads, m.dim, m.kv_rank)       # q_lat[h] = q_nope[h] @ uk[h]
+        self.uv = get("mix.uv", (m.heads * m.vdim, m.kv_rank)).view(m.heads, m.vdim, m.kv_rank)     # v[h] = out_lat[h] @ uv[h]^T
+        self.o = get("mix.o", (W, m.heads * m.vdim))
+        if f is None:
+            return
+        if f.kind == "dense":
+            self.up, self.down = get("mlp.up", (f.ff, W)), get("mlp.down", (W, f.ff))
+        else:
+            self.router = get("mlp.router", (f.experts, W), torch.float32)                            # the router runs in fp32
+            self.up = torch.cat([get(f"mlp.e{e}.up", (f.ff, W)) for e in range(f.experts)], dim=0).contiguous()
+            self.down = torch.cat([get(f"mlp.e{e}.down", (W, f.ff)) for e in range(f.experts)], dim=1).contiguous()
+
+
+class BupozenWeight:
+    def __init__(self, model_config, dtype: torch.dtype):
+        self.model_config, self.dtype = model_config, dtype
+        self.layers = [BupozenLayerWeight(i, model_config, dtype) for i in range(model_config.num_layers)]
+
+    def load_weights(self, getter: Callable, device="cuda"):
+        c = self.model_config
+        vs = (c.vocab_size, c.hidden_size)
+        self.wte = getter("embed", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.final_norm = getter("final.norm", (c.hidden_size,), self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.lm_head = getter("head", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.lm_head_sharded = False
+        for layer in self.layers:
+            layer.load_weights(getter, device)
+
+
+def load_bupozen_weights(model_config, dtype: torch.dtype, model_path: Optional[str], use_dummy: bool = False,
+                         getter: Optional[Callable] = None, device="cuda") -> BupozenWeight:
+    if getter is None:
+        getter = dummy_getter(device) if use_dummy else checkpoint_getter(model_path, device)
+    weight = BupozenWeight(model_config, dtype)
+    weight.load_weights(getter, device)
+    return weight
+
+
 # ---------------------------------------------------------------- getters
 def dummy_getter(device="cuda"):
     """weight.py:215-218: uniform(-1e-3, 1e-3), unseeded ("mainly for profiling")."""
@@ -112,7 +176,7 @@ def synthetic_getter(seed: int = 0, std: float = 0.02, device="cuda"):
         g = torch.Generator(device=device)
         g.manual_seed((seed * 1000003 + zlib.crc32(key.encode())) & 0x7FFFFFFF)
         t = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std
-        if key.endswith("norm.weight") or key.endswith("layernorm.weight"):
+        if key.endswith(("norm.weight", "layernorm.weight", ".norm", ".norm1")):
             t += 1.0
         return t.to(dtype)
     return get
@@ -140,7 +204,9 @@ def checkpoint_getter(model_path: str, device="cuda"):
 
         def get(key, shape, dtype):
             fname = index[key] if index is not None else st_files[0]
-            with safetensors.safe_open(os.path.join(model_path, fname), framework="pt", device=str(device)) as f:
+            dev = str(device)
+            with safetensors.safe_open(os.path.join(model_path, fname), framework="pt",
+                                       device="cpu" if dev.startswith("cpu") else dev) as f:
                 return f.get_tensor(key)
         return get
 

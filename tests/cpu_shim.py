@@ -129,6 +129,82 @@ def _swap_blocks(src_ids, dst_ids, is_swap_in, k_cache, v_cache, k_swap, v_swap)
     K.swap_blocks_inplace(src_ids, dst_ids, is_swap_in, k_cache, v_cache, k_swap, v_swap)
 
 
+
+# ---------------------------------------------------------------- stand-ins of the parallel-block / latent-attention kernels
+# (restated from the kernels' contracts in include/swiftllm_b200.h; fp32 arithmetic, results rounded to the storage dtype)
+def _add_rmsnorm_f32(residual, a, b, weight, eps, out=None):
+    if a is not None or b is not None:
+        y = a.float() if a is not None else torch.zeros_like(residual)
+        if b is not None:
+            y = y + b.float()
+        residual += y
+    o = (residual / torch.sqrt((residual * residual).mean(-1, keepdim=True) + eps) * weight.float()).to(weight.dtype)
+    if out is None:
+        return o
+    out.copy_(o)
+    return out
+
+
+def _rmsnorm_strided(x, weight, eps):
+    xf = x.float()
+    return (xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+
+
+def _relu2_inplace(x):
+    x.copy_((torch.relu(x.float()) ** 2).to(x.dtype))
+
+
+def _moe_route(logits, top):
+    vals, idx = torch.topk(logits, top, dim=-1)
+    return torch.zeros_like(logits).scatter_(1, idx, torch.softmax(vals, dim=-1))
+
+
+def _moe_relu2_scale_inplace(u, weights, ff):
+    T, E = weights.shape
+    u.copy_(((torch.relu(u.float()) ** 2).view(T, E, ff) * weights[:, :, None]).view(T, E * ff).to(u.dtype))
+
+
+def _rot_pairs(v, cos, sin, rot_dims):
+    """v [T, ..., d] fp32; pairs (2i, 2i+1) of the first rot_dims entries turn by the angles cos/sin [T, rot_dims/2]."""
+    if rot_dims == 0:
+        return v
+    shape = (v.shape[0],) + (1,) * (v.dim() - 2) + (rot_dims // 2,)
+    c, s = cos.view(shape), sin.view(shape)
+    u, w = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
+    out = v.clone()
+    out[..., 0:rot_dims:2] = u * c - w * s
+    out[..., 1:rot_dims:2] = w * c + u * s
+    return out
+
+
+def _cache_rows(cache, slot, block_table, seq, positions):
+    bs = cache.shape[2]
+    blocks = block_table[seq, torch.as_tensor(positions) // bs].long()
+    return cache[blocks, slot, torch.as_tensor(positions) % bs]
+
+
+def _latent_kv_store(dkv, norm_weight, cache, slot, block_table, st, r, dr, rot_dims, eps, cos, sin):
+    c = _rmsnorm_strided(dkv[:, :r], norm_weight, eps)
+    kr = _rot_pairs(dkv[:, r:].float(), cos, sin, rot_dims).to(dkv.dtype)
+    bs = cache.shape[2]
+    for t, (sq, p) in enumerate(zip(st.token_seq_ids.tolist(), st.token_positions.tolist())):
+        cache[int(block_table[sq, p // bs]), slot, p % bs] = torch.cat([c[t], kr[t]])
+
+
+def _latent_attention(q_lat, q_rot, gate, cache, slot, block_table, st, out, rot_dims, window, scale, cos, sin):
+    r = q_lat.shape[2]
+    qr = _rot_pairs(q_rot.float(), cos, sin, rot_dims)
+    qa = torch.cat([q_lat.float(), qr], dim=-1) * scale                     # [T, H, r + dr]
+    for t, (sq, p) in enumerate(zip(st.token_seq_ids.tolist(), st.token_positions.tolist())):
+        lo = max(0, p - window + 1) if window > 0 else 0
+        rows = _cache_rows(cache, slot, block_table, sq, list(range(lo, p + 1))).float()      # [n, r + dr]
+        pr = torch.softmax(qa[t] @ rows.T, dim=-1)                          # [H, n]
+        o = pr @ rows[:, :r]
+        if gate is not None:
+            o = o * torch.sigmoid(gate[t].float())[:, None]
+        out[t] = o.to(out.dtype)
+
+
 class GlooFusedAllReduce:
     """CPU stand-in of swiftllm_b200.worker.tp_comm.FusedAllReduce with the SAME observable semantics as the CUDA kernels
     (csrc/allreduce_norm.cu), exchanged over gloo: partials are summed in rank order in fp32, residual <- h(h(sum) + residual),
@@ -190,6 +266,13 @@ _PATCHES = [
     ("swiftllm_b200.worker.block_manager", "gather_allocated_blocks_and_unset", _gather_and_unset),
     ("swiftllm_b200.swiftllm_c", "swap_blocks", _swap_blocks),
     ("swiftllm_b200.swiftllm_c", "swap_blocks_device", _swap_blocks_device),
+    ("swiftllm_b200.worker.bupozen_model", "add_rmsnorm_f32", _add_rmsnorm_f32),
+    ("swiftllm_b200.worker.layers.latent_attention", "rmsnorm_strided", _rmsnorm_strided),
+    ("swiftllm_b200.worker.layers.latent_attention", "latent_kv_store", _latent_kv_store),
+    ("swiftllm_b200.worker.layers.latent_attention", "latent_attention", _latent_attention),
+    ("swiftllm_b200.worker.layers.feed_forward", "relu2_inplace", _relu2_inplace),
+    ("swiftllm_b200.worker.layers.feed_forward", "moe_route", _moe_route),
+    ("swiftllm_b200.worker.layers.feed_forward", "moe_relu2_scale_inplace", _moe_relu2_scale_inplace),
 ]
 
 
