@@ -60,6 +60,13 @@ class NativeLibraryError(RuntimeError):
     pass
 
 
+def _missing_symbol(name: str):
+    def call(*_args):
+        raise NativeLibraryError(f"{name} is not in {LIB_PATH} (it was built for a subset of the sources): "
+                                 "run `python -m swiftllm_b200.build`")
+    return call
+
+
 def lib() -> ctypes.CDLL:
     """Load (once) and return the native library; raises loudly when it is not built."""
     global _lib
@@ -70,7 +77,12 @@ def lib() -> ctypes.CDLL:
                 "swiftllm_b200 has no CPU or PyTorch fallback path.")
         l = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
-            fn = getattr(l, name)          # AttributeError if the symbol is missing
+            try:
+                fn = getattr(l, name)
+            except AttributeError:
+                # a library built for one model family only (build(only=...)): calling another family's kernel fails loudly
+                setattr(l, name, _missing_symbol(name))
+                continue
             fn.restype = res
             fn.argtypes = args
         if l.sllm_abi_version() != 1:

@@ -34,16 +34,25 @@ def _stale(out, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(verbose: bool = False, force: bool = False) -> str:
+def build(verbose: bool = False, force: bool = False, only=None) -> str:
+    """Compile what is stale and link the library.  `only`: an iterable of source names (a worker class's NATIVE_SOURCES) -
+    compile just those and link them together with whatever other objects are already up to date, so that the first run of
+    one model family in a fresh checkout does not pay for the kernels of the others.  Symbols of sources left out are
+    reported as missing when they are called (_lib.py); a later full build() compiles the rest and relinks."""
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "swiftllm_b200.h"))
-    jobs = []
+    jobs, fresh = [], []
+    wanted = None if only is None else set(only)
+    assert wanted is None or wanted <= set(sources()), f"unknown sources {sorted(wanted - set(sources()))}"
     for s in sources():
         src = os.path.join(CSRC, s)
         obj = os.path.join(OBJ, s[:-3] + ".o")
-        if force or _stale(obj, [src] + headers):
+        stale = force or _stale(obj, [src] + headers)
+        if stale and (wanted is None or s in wanted):
             jobs.append((src, obj))
+        if not stale or wanted is None or s in wanted:
+            fresh.append(obj)
 
     def compile_one(job):
         src, obj = job
@@ -60,7 +69,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(compile_one, jobs))
-    objs = [os.path.join(OBJ, s[:-3] + ".o") for s in sources()]
+    objs = fresh
     if jobs or _stale(LIB, objs):
         r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcudart"], capture_output=True, text=True)
         if r.returncode != 0:

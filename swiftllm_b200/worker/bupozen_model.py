@@ -38,6 +38,10 @@ _DTYPES = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torc
 
 
 class BupozenModel(PagedModelBase):
+    # CUDA sources this worker's kernels live in (build(only=...) compiles just these in a fresh checkout)
+    NATIVE_SOURCES = ("host.cu", "kvcache.cu", "parallel_block.cu", "latent_attn.cu")
+    DTYPES = tuple(_DTYPES)
+
     @torch.inference_mode()
     def __init__(self, engine_config: EngineConfig, model_config: Optional[BupozenModelConfig] = None):
         self.engine_config = engine_config

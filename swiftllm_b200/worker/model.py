@@ -75,6 +75,9 @@ def build_rope_tables(model_config: LlamaModelConfig, dtype: torch.dtype):
 
 
 class LlamaModel(PagedModelBase):
+    NATIVE_SOURCES = None           # every source of the library
+    DTYPES = tuple(_DTYPES)
+
     @torch.inference_mode()
     def __init__(self, engine_config: EngineConfig, model_config: Optional[LlamaModelConfig] = None):
         """`model_config` may be given directly (synthetic-weight runs); otherwise it is read from
