@@ -85,11 +85,170 @@ def parse():
     ap.add_argument("--parity-seqs", type=int, default=2, help="sequences re-run through the CPU oracle (tokens + logits)")
     ap.add_argument("--no-live-traffic", action="store_true", help="skip the ncu DRAM-byte measurement of the decode kernel")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--arch-compare", type=str, default="", metavar="SIZES",
+                    help="instead of the headline workload: prefill and decode throughput of the Bupozen worker beside the Llama "
+                         "worker at equal width / depth (random weights), with the attention kernels' roofline fractions; "
+                         "comma-separated sizes out of " + ",".join(ARCH_SIZES) + " or 'all'.  One JSON line per size and model.")
     ap.add_argument("--cpu-sample-seqs", type=int, default=8)
     ap.add_argument("--profile-range", type=int, default=0,
                     help="profiling aid: run this many eager decode steps inside cudaProfilerStart/Stop and exit "
                          "(use with ncu --profile-from-start off); prints no bench line")
     return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- --arch-compare
+# layer shapes of the size classes: width, heads, dense ff, experts x expert ff (top 4), latent attention like the published
+# latent-attention models (128 + 64 per head, 512-wide latent), sliding window, depth kept small (throughput is per layer)
+ARCH_SIZES = {
+    "w2048": dict(width=2048, heads=16, ff=8192, experts=16, eff=2048, top=4, window=1024, q_rank=768, layers=4, vocab=32000),
+    "w4096": dict(width=4096, heads=32, ff=14336, experts=32, eff=1792, top=4, window=2048, q_rank=1536, layers=4, vocab=32000),
+}
+
+
+def _arch_models(sz, dtype):
+    """(name, worker) pairs: Bupozen (layers alternate own-latent + dense ff / borrowed latent + MoE) and the closest existing
+    family, Llama with GQA (heads / 4 KV heads) and a gated ff of the same hidden size, same width / depth / vocabulary."""
+    import swiftllm_b200
+    from swiftllm_b200 import registry
+    from swiftllm_b200.worker.weight import synthetic_getter
+    W, H = sz["width"], sz["heads"]
+    layers = []
+    for i in range(sz["layers"]):
+        m = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": sz["q_rank"], "mask": {"size": sz["window"]},
+             "rot": {"base": 10000.0, "dims": 64}, "scale": 192 ** -0.5}
+        if i % 2 == 1:
+            m["kv_from"] = i - 1
+        ff = {"kind": "dense", "ff": sz["ff"]} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": sz["eff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}}
+        layers.append({"type": "latent_attention", "mixer": m, "mlp": ff})
+    bup = {"architecture": "Bupozen", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "layers": layers}
+    llama = dict(model_type="llama", num_hidden_layers=sz["layers"], num_attention_heads=H, num_key_value_heads=max(1, H // 4),
+                 hidden_size=W, intermediate_size=sz["ff"], vocab_size=sz["vocab"], max_position_embeddings=8192,
+                 rope_theta=10000.0, rms_norm_eps=1e-5, hidden_act="silu", rope_scaling=None)
+    for name, raw in (("bupozen", bup), ("llama", llama)):
+        ec = swiftllm_b200.EngineConfig(model_path="", use_dummy=False, block_size=16, gpu_mem_utilization=0.9, num_cpu_blocks=0,
+                                        max_seqs_in_block_table=128, max_blocks_per_seq=512, max_batch_size=64,
+                                        max_tokens_in_batch=16384, dtype=dtype)
+        model = registry.create_model(ec, registry.model_config_from_dict(raw))
+        model.load_weights(synthetic_getter(seed=0, std=0.02, device="cuda"))
+        model.init_kvcache_and_swap(64 * 4096 // 16 + 64)
+        yield name, raw, model
+        del model
+        torch.cuda.empty_cache()
+
+
+class _KernelTimer:
+    """CUDA-event timing of one kernel wrapper inside the real step (the wrapper is patched where the layer imported it)."""
+
+    def __init__(self, module, attr):
+        self.module, self.attr, self.orig, self.pairs = module, attr, getattr(module, attr), []
+
+    def __enter__(self):
+        def timed(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = self.orig(*a, **k)
+            e1.record()
+            self.pairs.append((e0, e1))
+            return out
+        setattr(self.module, self.attr, timed)
+        return self
+
+    def __exit__(self, *exc):
+        setattr(self.module, self.attr, self.orig)
+
+    def ms(self):
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in self.pairs)
+
+
+def run_arch_compare(args):
+    import importlib
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        peaks = {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "src": "measured"}
+    except OSError:
+        pass
+    torch.cuda.set_device(0)
+    names = list(ARCH_SIZES) if args.arch_compare == "all" else args.arch_compare.split(",")
+    n_prompts, prompt_len, dec_batch, ctx = 4, 2048, 64, 2048
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")           # > L2: written between timed iterations
+    for size in names:
+        sz = ARCH_SIZES[size]
+        for name, raw, model in _arch_models(sz, "bfloat16"):
+            g = torch.Generator().manual_seed(0)
+            prompts = [torch.randint(0, sz["vocab"], (prompt_len,), generator=g).tolist() for _ in range(n_prompts)]
+            if name == "bupozen":
+                mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.latent_attention"), ["latent_attention"]
+            else:
+                mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.transformer_layer"), ["prefill_attention", "paged_attention"]
+
+            def timed(fn, steps, warmup, after=None):
+                total_ms, kern = 0.0, 0.0
+                for it in range(warmup + steps):
+                    flush.fill_(it & 0xff)
+                    timers = [_KernelTimer(mod, a) for a in attrs]
+                    for t in timers:
+                        t.__enter__()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    for t in timers:
+                        t.__exit__()
+                    if it >= warmup:
+                        total_ms += e0.elapsed_time(e1)
+                        kern += sum(t.ms() for t in timers)
+                    if after:
+                        after()
+                return total_ms / steps, kern / steps
+
+            sids = list(range(n_prompts))
+            pre_ms, pre_attn_ms = timed(lambda: model.forward(prompts, sids, []), args.steps, args.warmup,
+                                        after=lambda: model.free_seqs_resources(sids))
+            # decode state: dec_batch sequences of ctx tokens in the cache (prefilled 4 at a time), then one token each per step
+            dids = list(range(dec_batch))
+            for i in range(0, dec_batch, 4):
+                model.forward([prompts[k % n_prompts][:ctx] for k in range(4)], dids[i:i + 4], [])
+            lens = [ctx] * dec_batch
+
+            def dec_step():
+                for k in range(dec_batch):
+                    lens[k] += 1
+                model.forward([[1]] * dec_batch, dids, lens)
+            dec_ms, dec_attn_ms = timed(dec_step, args.steps, args.warmup)
+            model.free_seqs_resources(dids)
+
+            L, H = sz["layers"], sz["heads"]
+            if name == "bupozen":
+                r, dr, Wn = 512, 64, sz["window"]
+                vis_pre = sum(min(p + 1, Wn) for p in range(prompt_len)) * n_prompts
+                fl_pre = L * vis_pre * H * (4 * r + 2 * dr)
+                by_pre = L * n_prompts * prompt_len * (r + dr + 2 * H * r + H * dr) * 2
+                vis_dec = dec_batch * min(ctx + 1, Wn)
+                fl_dec = L * vis_dec * H * (4 * r + 2 * dr)
+                by_dec = L * vis_dec * (r + dr) * 2
+            else:
+                D, nkv = sz["width"] // H, max(1, H // 4)
+                fl_pre = L * n_prompts * (prompt_len * (prompt_len + 1) // 2) * H * D * 4
+                by_pre = L * n_prompts * prompt_len * (2 * H + 2 * nkv) * D * 2
+                fl_dec = L * dec_batch * (ctx + 1) * H * D * 4
+                by_dec = L * dec_batch * (ctx + 1) * 2 * nkv * D * 2
+
+            def roof(fl, by, ms):
+                t_min = max(fl / (peaks["bf16_tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9)) * 1e3
+                return round(t_min / ms, 4) if ms > 0 else None
+            emit({"arch_compare": size, "model": name, "dtype": "bf16", "data": "synthetic", "layers": L,
+                  "prefill_tokens_per_s": round(n_prompts * prompt_len / pre_ms * 1e3, 1), "prefill_ms": round(pre_ms, 3),
+                  "decode_tokens_per_s": round(dec_batch / dec_ms * 1e3, 1), "decode_ms": round(dec_ms, 3),
+                  "attention_kernel": {"prefill_ms": round(pre_attn_ms, 3), "decode_ms": round(dec_attn_ms, 3),
+                                       "prefill_roofline_frac": roof(fl_pre, by_pre, pre_attn_ms),
+                                       "decode_roofline_frac": roof(fl_dec, by_dec, dec_attn_ms), "peaks": peaks["src"]},
+                  "config": {"prefill": f"{n_prompts}x{prompt_len}", "decode": f"batch {dec_batch} at context {ctx}",
+                             "l2": "256 MiB buffer written between timed iterations", "steps": args.steps, "warmup": args.warmup}})
 
 
 def model_dict(name, layers=0):
@@ -734,7 +893,10 @@ def emit(line: dict):
 def main():
     _protect_stdout()
     args = parse()
-    if args.impl == "reference":
+    if args.arch_compare:
+        with torch.inference_mode():
+            run_arch_compare(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         with torch.inference_mode():

@@ -5,6 +5,8 @@ per generated token).  Needs a B200 (there is no CPU path).
 
     python examples/offline.py --model-path /data/Llama-3-8B            # real checkpoint + its HF tokenizer
     python examples/offline.py --synthetic llama3-8b                     # seeded random weights, random token ids
+    python examples/offline.py --model-path /data/some-bupozen           # any family of the registry; without tokenizer files
+                                                                         # the prompts are random token ids
     ... --chunk 512        prefill the prompts in 512-token chunks through the paged cache (prefill_prefix_lens_list)
     ... --cuda-graph       replay decode steps from CUDA graphs
 """
@@ -55,7 +57,7 @@ def main():
     src = ap.add_mutually_exclusive_group(required=True)
     src.add_argument("--model-path", type=str, help="directory with config.json + safetensors / pytorch_model.bin + tokenizer")
     src.add_argument("--synthetic", type=str, choices=["llama3-8b", "llama3-70b"], help="architecture to fill with seeded random weights")
-    ap.add_argument("--dtype", type=str, default="bfloat16", choices=["float16", "bfloat16"])
+    ap.add_argument("--dtype", type=str, default="bfloat16", choices=["float16", "bfloat16", "float32"])
     ap.add_argument("--new-tokens", type=int, default=20)
     ap.add_argument("--chunk", type=int, default=0, help="chunked prefill: tokens of each prompt per forward call (0 = whole prompts)")
     ap.add_argument("--cuda-graph", action="store_true")
@@ -75,14 +77,19 @@ def main():
         input_ids = [torch.randint(0, mc.vocab_size, (n,), generator=g).tolist() for n in (9, 5, 1200, 6)]
         show = lambda ids: " ".join(map(str, ids))
     else:
-        from transformers import AutoTokenizer
-        model = swiftllm_b200.LlamaModel(ec)
+        model = swiftllm_b200.create_model(ec)          # the worker class is chosen from config.json
         model.load_weights()
-        tok = AutoTokenizer.from_pretrained(args.model_path)
-        prompts = ["Life blooms like a flower, far away", "one two three four five",
-                   "A B C D E F G H I J K L M N O P Q R S T U V", "To be or not to be,"]
-        input_ids = tok(prompts)["input_ids"]
-        show = lambda ids: tok.decode(ids, skip_special_tokens=True)
+        if any(os.path.exists(os.path.join(args.model_path, f)) for f in ("tokenizer.json", "tokenizer.model")):
+            from transformers import AutoTokenizer
+            tok = AutoTokenizer.from_pretrained(args.model_path)
+            prompts = ["Life blooms like a flower, far away", "one two three four five",
+                       "A B C D E F G H I J K L M N O P Q R S T U V", "To be or not to be,"]
+            input_ids = tok(prompts)["input_ids"]
+            show = lambda ids: tok.decode(ids, skip_special_tokens=True)
+        else:
+            g = torch.Generator().manual_seed(0)
+            input_ids = [torch.randint(0, model.model_config.vocab_size, (n,), generator=g).tolist() for n in (9, 5, 300, 6)]
+            show = lambda ids: " ".join(map(str, ids))
     num_blocks = model.profile_num_blocks()
     model.init_kvcache_and_swap(num_blocks)
     print(f"{num_blocks} KV blocks; model ready in {time.perf_counter() - t0:.1f} s")

@@ -65,3 +65,31 @@ def apply_step_result(step: PiggybackStep, prefilling: Sequence[PrefillProgress]
         if last:
             first[prefilling[i].seq_id] = tok
     return first, list(tokens[len(step.chunks):])
+
+
+def run_greedy(model, prompts: Sequence[Sequence[int]], new_tokens: int, max_tokens_in_step: int,
+               max_chunk: Optional[int] = None, seq_ids: Optional[Sequence[int]] = None) -> list:
+    """Greedy generation of `new_tokens` tokens per prompt, scheduled with plan_piggyback_step: every step carries one token of
+    each sequence that is already decoding plus as many prompt tokens as the budget allows, so prompts are prefilled in
+    portions beside running decodes.  Works with every worker class of the registry (they share forward()'s batch layout).
+    Sequence i uses block-table row seq_ids[i] (default i); the rows' blocks are given back before returning."""
+    seq_ids = list(range(len(prompts))) if seq_ids is None else list(seq_ids)
+    assert len(seq_ids) == len(prompts) and all(len(p) > 0 for p in prompts)
+    prefilling = [PrefillProgress(seq_id=s, prompt=list(p)) for s, p in zip(seq_ids, prompts)]
+    outputs = {s: [] for s in seq_ids}
+    lens = {s: len(p) for s, p in zip(seq_ids, prompts)}
+    decoding = []                       # seq ids whose prompt is in the cache and that still owe tokens
+    while any(p.remaining for p in prefilling) or decoding:
+        step = plan_piggyback_step([p for p in prefilling if p.remaining], decoding, [outputs[s][-1] for s in decoding],
+                                   [lens[s] + len(outputs[s]) for s in decoding], max_tokens_in_step, max_chunk)
+        active = [p for p in prefilling if p.remaining]
+        tokens = model.forward(step.input_ids_list, step.seq_ids_list, step.decoding_seq_lens_list,
+                               prefill_prefix_lens_list=step.prefill_prefix_lens_list)
+        first, decoded = apply_step_result(step, active, tokens)
+        for s, t in zip(decoding, decoded):
+            outputs[s].append(t)
+        for s, t in first.items():
+            outputs[s].append(t)
+        decoding = [s for s in seq_ids if outputs[s] and len(outputs[s]) < new_tokens]
+    model.free_seqs_resources(seq_ids)
+    return [outputs[s] for s in seq_ids]
