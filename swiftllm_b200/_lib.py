@@ -49,6 +49,7 @@ SIGNATURES = {
     "sllm_moe_route": (_I, [_P, _P, _L, _I, _I, _P]),
     "sllm_moe_relu2_scale_inplace": (_I, [_P, _P, _L, _I, _I, _I, _P]),
     "sllm_latent_kv_store": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _F, _I, _P]),
+    "sllm_latent_attention_set_simt": (_I, [_I]),
     "sllm_latent_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I,
                                    _I, _I, _I, _F, _I, _P]),
 }

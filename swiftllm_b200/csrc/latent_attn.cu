@@ -7,6 +7,7 @@
 // through the same kernel, so the result for a position does not depend on how its sequence was cut into steps.  A query at
 // position p attends to the positions max(0, p - window + 1) .. p (window <= 0: all of 0 .. p).
 // Softmax, the norm of the latent and the rotation run in fp32 for every storage type.
+#include "mma_helpers.cuh"
 #include "typed_io.cuh"
 
 namespace sllm {
@@ -144,6 +145,206 @@ __global__ void __launch_bounds__(LA_MAX_HPB * 32) latent_attn_kernel(
     }
 }
 
+
+// ------------------------------------------------------------------ attention, tensor-core path (16-bit storage)
+// One CTA per (token, group of 16 heads): the heads are the M dimension of the MMA tiles (all heads share the keys), 4 warps.
+// Per tile of LM_KT keys (raw cache rows, cp.async into shared memory, rows past the last visible key zero-filled):
+//   S[16, KT]  = Q[16, D] K^T          warp w: key columns 8w..8w+7 and 32+8w.., mma.m16n8k16 over D
+//   online softmax in fp32             warp w: heads 4w..4w+3, one or two keys per lane; P rounded to 16 bits (l sums the rounded P)
+//   O[16, r]  += P[16, KT] K[:, :r]    warp w: latent columns 8(w + 4i).., B fragments by ldmatrix.trans from the same key tile
+// Needs r % 16 == 0 and dr % 16 == 0 (16-byte rows for cp.async / ldmatrix); other shapes and float storage take the kernel above.
+constexpr int LM_KT = 64;
+
+template <typename T, int NT>      // NT: latent column tiles (8 wide) per warp, r <= 32 * NT
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(
+    const T* __restrict__ q_lat, int64_t ql_stride_t, int64_t ql_stride_h, const T* __restrict__ q_rot, int64_t qr_stride_t,
+    int64_t qr_stride_h, const float* __restrict__ cosb, const float* __restrict__ sinb, const T* __restrict__ gate,
+    int64_t gate_stride_t, const T* __restrict__ cache, int n_slots, int slot, int block_size,
+    const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
+    const int* __restrict__ tok_pos, T* __restrict__ out, int64_t out_stride_t, int64_t out_stride_h, int H, int r, int dr,
+    int rot_dims, int window, float scale) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int D = r + dr, LD = D + 8, LP = LM_KT + 8, LS = LM_KT + 1;
+    T* Qs = reinterpret_cast<T*>(smem_raw);                 // [16][LD]
+    T* Ks = Qs + 16 * LD;                                   // [KT][LD]
+    T* Ps = Ks + LM_KT * LD;                                // [16][LP]
+    float* Sf = reinterpret_cast<float*>(Ps + 16 * LP);     // [16][LS]
+    float* ms = Sf + 16 * LS;                               // [16] running max
+    float* ls = ms + 16;                                    // [16] running sum
+    float* al = ls + 16;                                    // [16] rescale factor of the current tile
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int64_t t = blockIdx.x;
+    const int h0 = blockIdx.y * 16;
+    const int pos = tok_pos[t];
+    const int* bt = block_table + (int64_t)tok_seq[t] * max_blocks_per_seq;
+
+    // queries of this head group: [q_lat | rotary(q_rot)], rows past H are zero
+    for (int hl = warp; hl < 16; hl += 4) {
+        const int h = h0 + hl;
+        T* qw = Qs + hl * LD;
+        if (h < H) {
+            const T* ql = q_lat + t * ql_stride_t + (int64_t)h * ql_stride_h;
+            const T* qr = q_rot + t * qr_stride_t + (int64_t)h * qr_stride_h;
+            for (int d = lane; d < r; d += 32) qw[d] = ql[d];
+            const int half = rot_dims >> 1;
+            for (int j = lane; j < dr; j += 32) {
+                float o;
+                if (j < rot_dims) {
+                    const int i = j >> 1;
+                    const float u = ldf(qr + 2 * i), v = ldf(qr + 2 * i + 1);
+                    const float c = cosb[t * half + i], s = sinb[t * half + i];
+                    o = (j & 1) ? v * c + u * s : u * c - v * s;
+                } else {
+                    o = ldf(qr + j);
+                }
+                stf(qw + r + j, o);
+            }
+        } else {
+            for (int d = lane; d < D; d += 32) stf(qw + d, 0.f);
+        }
+    }
+    if (threadIdx.x < 16) { ms[threadIdx.x] = -INFINITY; ls[threadIdx.x] = 0.f; }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    const int n_col_tiles = r >> 3;
+    const int chunks = D >> 3;             // 16-byte chunks per cache row
+    const uint32_t qs_a = smem_u32(Qs), ks_a = smem_u32(Ks), ps_a = smem_u32(Ps);
+
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    for (int base = lo; base <= pos; base += LM_KT) {
+        __syncthreads();                   // Ks / Ps of the previous tile are no longer read; Qs and the stats are written
+        const int nkeys = min(LM_KT, pos - base + 1);
+        for (int jj = warp; jj < LM_KT; jj += 4) {
+            const bool valid = jj < nkeys;
+            const int kp = valid ? base + jj : pos;
+            const T* src = cache + (((int64_t)bt[kp / block_size] * n_slots + slot) * block_size + kp % block_size) * D;
+            const uint32_t dst = ks_a + (uint32_t)(jj * LD) * 2u;
+            for (int c = lane; c < chunks; c += 32) cp_async16(dst + c * 16, src + c * 8, valid ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+
+        // ---- S = Q K^T: this warp's key columns 8w.. and 32 + 8w..
+        {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            const int j = lane >> 3;                                              // matrix of the x4 load this lane addresses
+            const uint32_t a_addr = qs_a + (uint32_t)((lane & 15) * LD + 8 * (lane >> 4)) * 2u;
+            const uint32_t b_addr = ks_a + (uint32_t)((8 * warp + 32 * (j >> 1) + (lane & 7)) * LD + 8 * (j & 1)) * 2u;
+            for (int kk = 0; kk < D; kk += 16) {
+                uint32_t a[4], b0, b1, b2, b3;
+                ldmatrix_x4(a_addr + kk * 2, a[0], a[1], a[2], a[3]);
+                ldmatrix_x4(b_addr + kk * 2, b0, b1, b2, b3);
+                mma_16816<T>(s0, a, b0, b1);
+                mma_16816<T>(s1, a, b2, b3);
+            }
+            const int c0 = 8 * warp + 2 * tq;
+            Sf[g * LS + c0] = s0[0]; Sf[g * LS + c0 + 1] = s0[1];
+            Sf[(g + 8) * LS + c0] = s0[2]; Sf[(g + 8) * LS + c0 + 1] = s0[3];
+            Sf[g * LS + 32 + c0] = s1[0]; Sf[g * LS + 32 + c0 + 1] = s1[1];
+            Sf[(g + 8) * LS + 32 + c0] = s1[2]; Sf[(g + 8) * LS + 32 + c0 + 1] = s1[3];
+        }
+        __syncthreads();
+
+        // ---- online softmax: this warp's heads 4w..4w+3
+        for (int row = 4 * warp; row < 4 * warp + 4; row++) {
+            const float x0 = lane < nkeys ? Sf[row * LS + lane] * scale : -INFINITY;
+            const float x1 = lane + 32 < nkeys ? Sf[row * LS + lane + 32] * scale : -INFINITY;
+            const float m_old = ms[row];
+            const float m_new = fmaxf(m_old, warp_max(fmaxf(x0, x1)));            // finite: key `base` is always visible
+            const T p0 = Traits<T>::from_f(lane < nkeys ? expf(x0 - m_new) : 0.f);
+            const T p1 = Traits<T>::from_f(lane + 32 < nkeys ? expf(x1 - m_new) : 0.f);
+            Ps[row * LP + lane] = p0;
+            Ps[row * LP + lane + 32] = p1;
+            const float sum = warp_sum(Traits<T>::to_f(p0) + Traits<T>::to_f(p1));
+            __syncwarp();
+            if (lane == 0) {
+                const float alpha = expf(m_old - m_new);                          // 0 on the first tile
+                ms[row] = m_new; ls[row] = ls[row] * alpha + sum; al[row] = alpha;
+            }
+        }
+        __syncthreads();
+
+        // ---- O = O * alpha + P K[:, :r]: this warp's latent column tiles w, w + 4, ...
+        {
+            const float a_lo = al[g], a_hi = al[g + 8];
+#pragma unroll
+            for (int i = 0; i < NT; i++) { acc[i][0] *= a_lo; acc[i][1] *= a_lo; acc[i][2] *= a_hi; acc[i][3] *= a_hi; }
+            const int j = lane >> 3;
+            const uint32_t a_addr = ps_a + (uint32_t)((lane & 15) * LP + 8 * (lane >> 4)) * 2u;
+            for (int ks = 0; ks < LM_KT && ks < nkeys; ks += 16) {
+                uint32_t a[4];
+                ldmatrix_x4(a_addr + ks * 2, a[0], a[1], a[2], a[3]);
+                const uint32_t row_addr = ks_a + (uint32_t)((ks + 8 * (j & 1) + (lane & 7)) * LD) * 2u;
+#pragma unroll
+                for (int i = 0; i < NT; i += 2) {
+                    const int ct0 = warp + 4 * i, ct1 = warp + 4 * (i + 1);
+                    if (ct0 >= n_col_tiles) break;
+                    const int ct = (j >> 1) ? (ct1 < n_col_tiles ? ct1 : ct0) : ct0;
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(row_addr + ct * 16, b0, b1, b2, b3);
+                    mma_16816<T>(acc[i], a, b0, b1);
+                    if (ct1 < n_col_tiles) mma_16816<T>(acc[i + 1], a, b2, b3);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NT; i++) {
+        const int ct = warp + 4 * i;
+        if (ct >= n_col_tiles) break;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int hl = g + 8 * half, h = h0 + hl;
+            if (h >= H) continue;
+            float gt = 1.f;
+            if (gate != nullptr) gt = 1.f / (1.f + expf(-ldf(gate + t * gate_stride_t + h)));
+            const float f = gt / ls[hl];
+            T* o = out + t * out_stride_t + (int64_t)h * out_stride_h + ct * 8 + 2 * tq;
+            stf(o, acc[i][2 * half] * f);
+            stf(o + 1, acc[i][2 * half + 1] * f);
+        }
+    }
+}
+
+template <typename T, int NT>
+static int launch_latent_attn_mma(const void* q_lat, int64_t ql_st, int64_t ql_sh, const void* q_rot, int64_t qr_st, int64_t qr_sh,
+                                  const void* cosb, const void* sinb, const void* gate, int64_t gate_st, const void* cache,
+                                  int n_slots, int slot, int block_size, const void* block_table, int max_blocks_per_seq,
+                                  const void* tok_seq, const void* tok_pos, void* out, int64_t out_st, int64_t out_sh,
+                                  int64_t num_tokens, int H, int r, int dr, int rot_dims, int window, float scale,
+                                  cudaStream_t stream) {
+    const int D = r + dr;
+    const size_t smem = ((size_t)(16 + LM_KT) * (D + 8) + 16 * (LM_KT + 8)) * 2 + (16 * (LM_KT + 1) + 48) * sizeof(float);
+    SLLM_REQUIRE(smem <= 200 * 1024, "latent_attention: r + dr = %d needs %zu bytes of shared memory", D, smem);
+    static unsigned long long configured = 0;
+    auto kern = latent_attn_mma_kernel<T, NT>;
+    if (first_use_on_this_device(configured)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        SLLM_REQUIRE(e == cudaSuccess, "latent_attention: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
+    dim3 grid((unsigned)num_tokens, (unsigned)cdiv(H, 16));
+    kern<<<grid, 128, smem, stream>>>(
+        (const T*)q_lat, ql_st, ql_sh, (const T*)q_rot, qr_st, qr_sh, (const float*)cosb, (const float*)sinb, (const T*)gate,
+        gate_st, (const T*)cache, n_slots, slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq,
+        (const int*)tok_pos, (T*)out, out_st, out_sh, H, r, dr, rot_dims, window, scale);
+    return check_launch("latent_attention (mma)");
+}
+
+template <typename T> struct LatentMma {
+    template <typename... A> static int run(int r, A... a) {
+        if (r <= 128) return launch_latent_attn_mma<T, 4>(a...);
+        if (r <= 256) return launch_latent_attn_mma<T, 8>(a...);
+        return launch_latent_attn_mma<T, 16>(a...);
+    }
+};
+template <> struct LatentMma<float> {
+    template <typename... A> static int run(int, A...) { set_error("latent_attention: no tensor-core path for float storage"); return 1; }
+};
+
 template <typename T, int KR>
 static int launch_latent_attn(const void* q_lat, int64_t ql_st, int64_t ql_sh, const void* q_rot, int64_t qr_st, int64_t qr_sh,
                               const void* cosb, const void* sinb, const void* gate, int64_t gate_st, const void* cache,
@@ -173,7 +374,16 @@ static int launch_latent_attn(const void* q_lat, int64_t ql_st, int64_t ql_sh, c
 
 using namespace sllm;
 
+// tests and A/B timing: 1 = always take the CUDA-core kernel (process-wide; set through sllm_latent_attention_set_simt)
+static int sllm_latent_attention_force_simt = 0;
+
 extern "C" {
+
+int sllm_latent_attention_set_simt(int on) {
+    const int old = sllm_latent_attention_force_simt;
+    sllm_latent_attention_force_simt = on ? 1 : 0;
+    return old;
+}
 
 int sllm_latent_kv_store(const void* dkv, int64_t row_stride, const void* norm_weight, const void* cosb, const void* sinb,
                          const void* tok_seq, const void* tok_pos, const void* block_table, int max_blocks_per_seq,
@@ -210,6 +420,11 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
 #define SLLM_LA_ARGS q_lat, q_lat_stride_t, q_lat_stride_h, q_rot, q_rot_stride_t, q_rot_stride_h, cosb, sinb, gate,            \
                      gate_stride_t, cache, n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out,   \
                      out_stride_t, out_stride_h, num_tokens, num_heads, r, dr, rot_dims, window, scale, (cudaStream_t)stream
+    // 16-bit storage and 16-element-aligned rows: tensor cores; everything else: the fp32 CUDA-core kernel
+    const bool mma = dtype != SLLM_F32 && r % 16 == 0 && dr % 16 == 0 && !sllm_latent_attention_force_simt;
+    if (mma) {
+        SLLM_DISPATCH_DTYPE_F32(dtype, return (LatentMma<T>::run(r, SLLM_LA_ARGS)));
+    }
     SLLM_DISPATCH_DTYPE_F32(dtype, {
         if (r <= 64) return (launch_latent_attn<T, 2>(SLLM_LA_ARGS));
         if (r <= 128) return (launch_latent_attn<T, 4>(SLLM_LA_ARGS));

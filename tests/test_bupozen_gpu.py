@@ -153,7 +153,11 @@ def _plain_attention(q_lat, q_rot, gate, rows, pos, window, scale, base, dims, r
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,r,dr,dims,window,bs", [(3, 24, 6, 4, 7, 4), (11, 72, 4, 4, 33, 16), (2, 136, 8, 8, 0, 8), (9, 40, 2, 0, 32, 32)])
+@pytest.mark.parametrize("H,r,dr,dims,window,bs", [
+    (3, 24, 6, 4, 7, 4), (11, 72, 4, 4, 33, 16), (2, 136, 8, 8, 0, 8), (9, 40, 2, 0, 32, 32),      # CUDA-core kernel
+    # 16-element-aligned rows: with 16-bit storage these take the tensor-core kernel (1, 2 and 3 head groups, whole and partial
+    # column tiles per warp, windows that end inside / at the edge of / beyond a 64-key tile)
+    (20, 64, 16, 16, 100, 16), (5, 128, 32, 24, 0, 8), (16, 512, 64, 64, 64, 16), (33, 208, 48, 48, 65, 4), (4, 16, 16, 0, 63, 32)])
 def test_latent_attention_standout_keys(dtype, H, r, dr, dims, window, bs):
     """Among hundreds of small keys ONE key per query scores far above the rest, placed where an off-by-one shows: far back,
     the first and last position a window keeps, the position just outside it, both sides of a block border, position 0.  A
@@ -195,6 +199,34 @@ def test_latent_attention_standout_keys(dtype, H, r, dr, dims, window, bs):
         ref = _plain_attention(q_lat[t].float(), q_wide[t, :, 5:].float(), gate[t, 3:].float(), rows[s].float(), pos, window, scale,
                                base, dims, r)
         assert C.rel_err(out[t, :, :r], ref) < (1e-4 if dtype == torch.float32 else 3e-2), (s, pos, key)
+
+
+def test_tensor_core_and_cuda_core_attention_agree():
+    """The same bf16 inputs through both kernels (the library switch forces the CUDA-core one)."""
+    from swiftllm_b200 import _lib
+    from swiftllm_b200.worker.kernels.latent_attn import latent_attention
+    H, r, dr, bs, n = 24, 96, 32, 16, 200
+    g = torch.Generator().manual_seed(5)
+    cache, bt = _paged([n], bs, r + dr, torch.bfloat16, seed=5)
+    cache.copy_((torch.randn(cache.shape, generator=g) * 0.5).to(torch.bfloat16))
+    pos = [0, 1, 15, 16, 63, 64, 65, 127, 128, 199]
+    T = len(pos)
+    q_lat, q_rot = (torch.randn(T, H, d, generator=g).to(torch.bfloat16).to(DEV) for d in (r, dr))
+    gate = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    ang = torch.tensor(pos, dtype=torch.float64)[:, None] * torch.tensor([10.0 ** (-2.0 * i / 32) for i in range(16)], dtype=torch.float64)
+    st = types.SimpleNamespace(token_seq_ids=torch.zeros(T, dtype=torch.int32, device=DEV),
+                               token_positions=torch.tensor(pos, dtype=torch.int32, device=DEV))
+    outs = []
+    for simt in (0, 1):
+        old = _lib.lib().sllm_latent_attention_set_simt(simt)
+        try:
+            out = torch.empty(T, H, r, dtype=torch.bfloat16, device=DEV)
+            latent_attention(q_lat, q_rot, gate, cache.to(DEV), 1, bt.to(DEV), st, out, 32, 70, 0.2,
+                             torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV))
+            outs.append(out.float().cpu())
+        finally:
+            _lib.lib().sllm_latent_attention_set_simt(old)
+    assert C.rel_err(outs[0], outs[1]) < 1e-2
 
 
 # ---------------------------------------------------------------- the worker
@@ -241,4 +273,18 @@ def test_bfloat16_worker_close_to_fp32_oracle():
     m = C.make_worker(_make, cfg, t, dtype="bfloat16")
     whole = C.run_portions(m, toks, 0, [33])
     cut = C.run_portions(m, toks, 1, [5, 2, 1, 1, 24])
+    assert C.rel_err(whole, ref) < 3e-2 and C.rel_err(cut, ref) < 3e-2 and C.rel_err(cut, whole) < 2e-2
+
+
+def test_bfloat16_worker_on_tensor_core_shapes():
+    """Latent sizes that are multiples of 16 send the bf16 worker through the tensor-core attention kernel."""
+    cfg = C.config([(C.mixer(heads=3, kv_rank=32, rot_dim=16, dims=16, window=70), C.DENSE),
+                    (C.mixer(heads=18, kv_rank=32, rot_dim=16, dims=16, window=9, kv_from=0), C.moe()),
+                    (C.mixer(heads=2, kv_rank=144, rot_dim=32, dims=20, window=100), None)], width=64)
+    t = O.random_tensors(cfg, seed=12)
+    toks = C.tokens_for(cfg, 150, 12)
+    ref = O.forward(cfg, t, toks)[-40:]
+    m = C.make_worker(_make, cfg, t, dtype="bfloat16", block_size=8, num_blocks=60)
+    whole = C.run_portions(m, toks, 0, [150])[-40:]
+    cut = C.run_portions(m, toks, 1, [61, 4, 64, 2, 1, 1, 17])[-40:]
     assert C.rel_err(whole, ref) < 3e-2 and C.rel_err(cut, ref) < 3e-2 and C.rel_err(cut, whole) < 2e-2
