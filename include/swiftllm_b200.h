@@ -247,12 +247,15 @@ int sllm_latent_kv_store(const void* dkv, int64_t row_stride, const void* norm_w
 /* 16-bit dtypes with r % 16 == 0 and dr % 16 == 0 run on tensor cores (mma.sync over the heads of a token); other shapes and
  * SLLM_F32 run the fp32 CUDA-core kernel.  sllm_latent_attention_set_simt(1) forces the latter (returns the old setting). */
 int sllm_latent_attention_set_simt(int on);
+/* num_splits > 1 with split_workspace (fp32 [T, num_heads, num_splits, r + 2], device) lets the tensor-core kernel share a
+ * query's visible keys between num_splits CTAs (steps with few tokens), merged by a second kernel; ignored by the other path. */
 int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_lat_stride_h, const void* q_rot,
                           int64_t q_rot_stride_t, int64_t q_rot_stride_h, const void* cosb, const void* sinb,
                           const void* gate, int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos,
                           void* out, int64_t out_stride_t, int64_t out_stride_h, int64_t num_tokens, int num_heads, int r,
-                          int dr, int rot_dims, int window, float scale, sllm_dtype_t dtype, sllm_stream_t stream);
+                          int dr, int rot_dims, int window, float scale, int num_splits, void* split_workspace,
+                          sllm_dtype_t dtype, sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     int64_t gate_stride_t, const T* __restrict__ cache, int n_slots, int slot, int block_size,
     const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
     const int* __restrict__ tok_pos, T* __restrict__ out, int64_t out_stride_t, int64_t out_stride_h, int H, int r, int dr,
-    int rot_dims, int window, float scale) {
+    int rot_dims, int window, float scale, int nsplit, float* __restrict__ partial) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int D = r + dr, LD = D + 8, LP = LM_KT + 8, LS = LM_KT + 1;
     T* Qs = reinterpret_cast<T*>(smem_raw);                 // [16][LD]
@@ -212,8 +212,14 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const int chunks = D >> 3;             // 16-byte chunks per cache row
     const uint32_t qs_a = smem_u32(Qs), ks_a = smem_u32(Ks), ps_a = smem_u32(Ps);
 
+    // gridDim.z CTAs share the visible keys of a (token, head group): CTA z takes a contiguous run of key tiles and, when
+    // nsplit > 1, leaves (unnormalised sum, running max, running sum) in `partial` for latent_attn_combine_kernel
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    for (int base = lo; base <= pos; base += LM_KT) {
+    const int tiles = (pos - lo + LM_KT) / LM_KT;
+    const int per_split = (tiles + nsplit - 1) / nsplit;
+    const int tile_end = min(tiles, ((int)blockIdx.z + 1) * per_split);
+    for (int tile = blockIdx.z * per_split; tile < tile_end; tile++) {
+        const int base = lo + tile * LM_KT;
         __syncthreads();                   // Ks / Ps of the previous tile are no longer read; Qs and the stats are written
         const int nkeys = min(LM_KT, pos - base + 1);
         for (int jj = warp; jj < LM_KT; jj += 4) {
@@ -300,6 +306,13 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         for (int half = 0; half < 2; half++) {
             const int hl = g + 8 * half, h = h0 + hl;
             if (h >= H) continue;
+            if (nsplit > 1) {
+                float* pr = partial + ((t * H + h) * nsplit + blockIdx.z) * (r + 2);
+                pr[ct * 8 + 2 * tq] = acc[i][2 * half];
+                pr[ct * 8 + 2 * tq + 1] = acc[i][2 * half + 1];
+                if (ct == 0 && tq == 0) { pr[r] = ms[hl]; pr[r + 1] = ls[hl]; }
+                continue;
+            }
             float gt = 1.f;
             if (gate != nullptr) gt = 1.f / (1.f + expf(-ldf(gate + t * gate_stride_t + h)));
             const float f = gt / ls[hl];
@@ -310,13 +323,39 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     }
 }
 
+// One warp per (token, head): merge the key splits.  partial [T, H, nsplit, r + 2] = (sum_j e^(s_j - m) c_j, m, sum_j e^(s_j - m));
+// a split that saw no key has m = -inf and contributes nothing.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* __restrict__ partial, const T* __restrict__ gate,
+                                                                  int64_t gate_stride_t, T* __restrict__ out, int64_t out_stride_t,
+                                                                  int64_t out_stride_h, int64_t num_tokens, int H, int r, int nsplit) {
+    const int lane = threadIdx.x & 31;
+    const int64_t idx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (idx >= num_tokens * H) return;
+    const int64_t t = idx / H;
+    const int h = (int)(idx - t * H);
+    const float* pr = partial + idx * nsplit * (r + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < nsplit; z++) M = fmaxf(M, pr[z * (r + 2) + r]);
+    float L = 0.f;
+    for (int z = 0; z < nsplit; z++) L += expf(pr[z * (r + 2) + r] - M) * pr[z * (r + 2) + r + 1];
+    float gt = 1.f;
+    if (gate != nullptr) gt = 1.f / (1.f + expf(-ldf(gate + t * gate_stride_t + h)));
+    T* o = out + t * out_stride_t + (int64_t)h * out_stride_h;
+    for (int d = lane; d < r; d += 32) {
+        float a = 0.f;
+        for (int z = 0; z < nsplit; z++) a += expf(pr[z * (r + 2) + r] - M) * pr[z * (r + 2) + d];
+        stf(o + d, a / L * gt);
+    }
+}
+
 template <typename T, int NT>
 static int launch_latent_attn_mma(const void* q_lat, int64_t ql_st, int64_t ql_sh, const void* q_rot, int64_t qr_st, int64_t qr_sh,
                                   const void* cosb, const void* sinb, const void* gate, int64_t gate_st, const void* cache,
                                   int n_slots, int slot, int block_size, const void* block_table, int max_blocks_per_seq,
                                   const void* tok_seq, const void* tok_pos, void* out, int64_t out_st, int64_t out_sh,
                                   int64_t num_tokens, int H, int r, int dr, int rot_dims, int window, float scale,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, int nsplit, void* partial) {
     const int D = r + dr;
     const size_t smem = ((size_t)(16 + LM_KT) * (D + 8) + 16 * (LM_KT + 8)) * 2 + (16 * (LM_KT + 1) + 48) * sizeof(float);
     SLLM_REQUIRE(smem <= 200 * 1024, "latent_attention: r + dr = %d needs %zu bytes of shared memory", D, smem);
@@ -326,12 +365,18 @@ static int launch_latent_attn_mma(const void* q_lat, int64_t ql_st, int64_t ql_s
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         SLLM_REQUIRE(e == cudaSuccess, "latent_attention: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     }
-    dim3 grid((unsigned)num_tokens, (unsigned)cdiv(H, 16));
+    dim3 grid((unsigned)num_tokens, (unsigned)cdiv(H, 16), (unsigned)nsplit);
     kern<<<grid, 128, smem, stream>>>(
         (const T*)q_lat, ql_st, ql_sh, (const T*)q_rot, qr_st, qr_sh, (const float*)cosb, (const float*)sinb, (const T*)gate,
         gate_st, (const T*)cache, n_slots, slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq,
-        (const int*)tok_pos, (T*)out, out_st, out_sh, H, r, dr, rot_dims, window, scale);
-    return check_launch("latent_attention (mma)");
+        (const int*)tok_pos, (T*)out, out_st, out_sh, H, r, dr, rot_dims, window, scale, nsplit, (float*)partial);
+    if (int rc = check_launch("latent_attention (mma)")) return rc;
+    if (nsplit > 1) {
+        latent_attn_combine_kernel<T><<<(unsigned)cdiv(num_tokens * H, 4), 128, 0, stream>>>(
+            (const float*)partial, (const T*)gate, gate_st, (T*)out, out_st, out_sh, num_tokens, H, r, nsplit);
+        return check_launch("latent_attention (combine)");
+    }
+    return 0;
 }
 
 template <typename T> struct LatentMma {
@@ -408,7 +453,8 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
                           const void* gate, int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos,
                           void* out, int64_t out_stride_t, int64_t out_stride_h, int64_t num_tokens, int num_heads, int r,
-                          int dr, int rot_dims, int window, float scale, sllm_dtype_t dtype, sllm_stream_t stream) {
+                          int dr, int rot_dims, int window, float scale, int num_splits, void* split_workspace,
+                          sllm_dtype_t dtype, sllm_stream_t stream) {
     SLLM_REQUIRE(num_tokens >= 0 && num_heads > 0 && r > 0 && r <= 512 && dr >= 0 && rot_dims >= 0 && rot_dims <= dr &&
                  rot_dims % 2 == 0, "latent_attention: bad shape (heads %d, r %d <= 512, dr %d, rot_dims %d)", num_heads, r, dr,
                  rot_dims);
@@ -423,7 +469,8 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
     // 16-bit storage and 16-element-aligned rows: tensor cores; everything else: the fp32 CUDA-core kernel
     const bool mma = dtype != SLLM_F32 && r % 16 == 0 && dr % 16 == 0 && !sllm_latent_attention_force_simt;
     if (mma) {
-        SLLM_DISPATCH_DTYPE_F32(dtype, return (LatentMma<T>::run(r, SLLM_LA_ARGS)));
+        const int nsplit = (num_splits > 1 && split_workspace != nullptr) ? (num_splits > 64 ? 64 : num_splits) : 1;
+        SLLM_DISPATCH_DTYPE_F32(dtype, return (LatentMma<T>::run(r, SLLM_LA_ARGS, nsplit, split_workspace)));
     }
     SLLM_DISPATCH_DTYPE_F32(dtype, {
         if (r <= 64) return (launch_latent_attn<T, 2>(SLLM_LA_ARGS));

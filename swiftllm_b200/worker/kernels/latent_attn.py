@@ -18,6 +18,23 @@ def latent_kv_store(dkv: torch.Tensor, norm_weight: torch.Tensor, cache: torch.T
         _lib.stream()), "latent_kv_store")
 
 
+_SM_COUNT = {}
+
+
+def _num_splits(T: int, H: int, window: int, dtype) -> int:
+    """Key splits for the tensor-core kernel: enough CTAs for two per SM when the step has few tokens (decoding); never more
+    than the 64-key tiles a window can hold (16 when there is no window)."""
+    if dtype == torch.float32:
+        return 1
+    dev = torch.cuda.current_device()
+    if dev not in _SM_COUNT:
+        _SM_COUNT[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    ctas = T * ((H + 15) // 16)
+    want = (2 * _SM_COUNT[dev] + ctas - 1) // ctas
+    most = (window + 63) // 64 + 1 if window > 0 else 16
+    return max(1, min(want, most, 32))
+
+
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, gate, cache: torch.Tensor, slot: int, block_table: torch.Tensor,
                      infer_state, out: torch.Tensor, rot_dims: int, window: int, scale: float, cos: torch.Tensor, sin: torch.Tensor):
     """q_lat [T, H, r], q_rot [T, H, dr] (un-rotated), gate [T, H] logits or None, out [T, H, r]; views with arbitrary token /
@@ -28,10 +45,12 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, gate, cache: torc
     assert cache.shape[3] == r + dr and cache.dtype == q_lat.dtype
     assert gate is None or (gate.shape == (T, H) and gate.stride(1) == 1)
     _lib.require_device(q_lat)
+    nsplit = _num_splits(T, H, window, q_lat.dtype)
+    ws = torch.empty((T, H, nsplit, r + 2), dtype=torch.float32, device=q_lat.device) if nsplit > 1 else None
     _lib.check(_lib.lib().sllm_latent_attention(
         q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1),
         _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(gate), gate.stride(0) if gate is not None else 0,
         cache.data_ptr(), cache.shape[1], slot, cache.shape[2], block_table.data_ptr(), block_table.shape[1],
         infer_state.token_seq_ids.data_ptr(), infer_state.token_positions.data_ptr(),
-        out.data_ptr(), out.stride(0), out.stride(1), T, H, r, dr, rot_dims, window, scale,
+        out.data_ptr(), out.stride(0), out.stride(1), T, H, r, dr, rot_dims, window, scale, nsplit, _lib.ptr(ws),
         _lib.dtype_tag_f32(q_lat.dtype), _lib.stream()), "latent_attention")
