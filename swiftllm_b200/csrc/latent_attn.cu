@@ -235,17 +235,32 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
 
         // ---- S = Q K^T: this warp's key columns 8w.. and 32 + 8w..
         {
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            // two accumulators per key column tile (even / odd 16-wide slices of D): half the length of the dependent MMA chain
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};
             const int j = lane >> 3;                                              // matrix of the x4 load this lane addresses
             const uint32_t a_addr = qs_a + (uint32_t)((lane & 15) * LD + 8 * (lane >> 4)) * 2u;
             const uint32_t b_addr = ks_a + (uint32_t)((8 * warp + 32 * (j >> 1) + (lane & 7)) * LD + 8 * (j & 1)) * 2u;
-            for (int kk = 0; kk < D; kk += 16) {
+            int kk = 0;
+            for (; kk + 32 <= D; kk += 32) {
+                uint32_t a[4], c[4], b0, b1, b2, b3, d0, d1, d2, d3;
+                ldmatrix_x4(a_addr + kk * 2, a[0], a[1], a[2], a[3]);
+                ldmatrix_x4(b_addr + kk * 2, b0, b1, b2, b3);
+                ldmatrix_x4(a_addr + kk * 2 + 32, c[0], c[1], c[2], c[3]);
+                ldmatrix_x4(b_addr + kk * 2 + 32, d0, d1, d2, d3);
+                mma_16816<T>(s0, a, b0, b1);
+                mma_16816<T>(s1, a, b2, b3);
+                mma_16816<T>(u0, c, d0, d1);
+                mma_16816<T>(u1, c, d2, d3);
+            }
+            if (kk < D) {
                 uint32_t a[4], b0, b1, b2, b3;
                 ldmatrix_x4(a_addr + kk * 2, a[0], a[1], a[2], a[3]);
                 ldmatrix_x4(b_addr + kk * 2, b0, b1, b2, b3);
                 mma_16816<T>(s0, a, b0, b1);
                 mma_16816<T>(s1, a, b2, b3);
             }
+#pragma unroll
+            for (int e = 0; e < 4; e++) { s0[e] += u0[e]; s1[e] += u1[e]; }
             const int c0 = 8 * warp + 2 * tq;
             Sf[g * LS + c0] = s0[0]; Sf[g * LS + c0 + 1] = s0[1];
             Sf[(g + 8) * LS + c0] = s0[2]; Sf[(g + 8) * LS + c0 + 1] = s0[3];

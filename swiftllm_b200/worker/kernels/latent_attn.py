@@ -22,15 +22,15 @@ _SM_COUNT = {}
 
 
 def _num_splits(T: int, H: int, window: int, dtype) -> int:
-    """Key splits for the tensor-core kernel: enough CTAs for two per SM when the step has few tokens (decoding); never more
-    than the 64-key tiles a window can hold (16 when there is no window)."""
+    """Key splits for the tensor-core kernel: as many CTAs as fit at once (two per SM) when the step has few tokens (decoding),
+    never a second wave; never more than the 64-key tiles a window can hold (16 when there is no window)."""
     if dtype == torch.float32:
         return 1
     dev = torch.cuda.current_device()
     if dev not in _SM_COUNT:
         _SM_COUNT[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
     ctas = T * ((H + 15) // 16)
-    want = (2 * _SM_COUNT[dev] + ctas - 1) // ctas
+    want = (2 * _SM_COUNT[dev]) // ctas
     most = (window + 63) // 64 + 1 if window > 0 else 16
     return max(1, min(want, most, 32))
 
