@@ -220,6 +220,12 @@ def run_arch_compare(args):
                     lens[k] += 1
                 model.forward([[1]] * dec_batch, dids, lens)
             dec_ms, dec_attn_ms = timed(dec_step, args.steps, args.warmup)
+            # the same steps replayed from a CUDA graph (both workers capture pure-decode steps); no per-kernel events in a graph
+            model.engine_config.use_cuda_graph = True
+            attrs_saved, attrs[:] = list(attrs), []
+            graph_ms, _ = timed(dec_step, args.steps, args.warmup)
+            attrs[:] = attrs_saved
+            model.engine_config.use_cuda_graph = False
             model.free_seqs_resources(dids)
 
             L, H = sz["layers"], sz["heads"]
@@ -244,6 +250,7 @@ def run_arch_compare(args):
             emit({"arch_compare": size, "model": name, "dtype": "bf16", "data": "synthetic", "layers": L,
                   "prefill_tokens_per_s": round(n_prompts * prompt_len / pre_ms * 1e3, 1), "prefill_ms": round(pre_ms, 3),
                   "decode_tokens_per_s": round(dec_batch / dec_ms * 1e3, 1), "decode_ms": round(dec_ms, 3),
+                  "decode_graph_tokens_per_s": round(dec_batch / graph_ms * 1e3, 1), "decode_graph_ms": round(graph_ms, 3),
                   "attention_kernel": {"prefill_ms": round(pre_attn_ms, 3), "decode_ms": round(dec_attn_ms, 3),
                                        "prefill_roofline_frac": roof(fl_pre, by_pre, pre_attn_ms),
                                        "decode_roofline_frac": roof(fl_dec, by_dec, dec_attn_ms), "peaks": peaks["src"]},

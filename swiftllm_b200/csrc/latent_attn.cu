@@ -147,16 +147,17 @@ __global__ void __launch_bounds__(LA_MAX_HPB * 32) latent_attn_kernel(
 
 
 // ------------------------------------------------------------------ attention, tensor-core path (16-bit storage)
-// One CTA per (token, group of 16 heads): the heads are the M dimension of the MMA tiles (all heads share the keys), 4 warps.
+// One CTA per (token, group of 16 heads): the heads are the M dimension of the MMA tiles (all heads share the keys), 8 warps.
 // Per tile of LM_KT keys (raw cache rows, cp.async into shared memory, rows past the last visible key zero-filled):
-//   S[16, KT]  = Q[16, D] K^T          warp w: key columns 8w..8w+7 and 32+8w.., mma.m16n8k16 over D
-//   online softmax in fp32             warp w: heads 4w..4w+3, one or two keys per lane; P rounded to 16 bits (l sums the rounded P)
-//   O[16, r]  += P[16, KT] K[:, :r]    warp w: latent columns 8(w + 4i).., B fragments by ldmatrix.trans from the same key tile
+//   S[16, KT]  = Q[16, D] K^T          warp w: key columns 8w..8w+7, mma.m16n8k16 over D (two accumulators: even / odd slices)
+//   online softmax in fp32             warp w: heads 2w, 2w+1, two keys per lane; P rounded to 16 bits (l sums the rounded P)
+//   O[16, r]  += P[16, KT] K[:, :r]    warp w: latent columns 8(w + 8i).., B fragments by ldmatrix.trans from the same key tile
 // Needs r % 16 == 0 and dr % 16 == 0 (16-byte rows for cp.async / ldmatrix); other shapes and float storage take the kernel above.
 constexpr int LM_KT = 64;
+constexpr int LM_NW = 8;           // warps per CTA = key column tiles per key tile (LM_KT / 8)
 
-template <typename T, int NT>      // NT: latent column tiles (8 wide) per warp, r <= 32 * NT
-__global__ void __launch_bounds__(128) latent_attn_mma_kernel(
+template <typename T, int NT>      // NT: latent column tiles (8 wide) per warp, r <= 64 * NT
+__global__ void __launch_bounds__(LM_NW * 32) latent_attn_mma_kernel(
     const T* __restrict__ q_lat, int64_t ql_stride_t, int64_t ql_stride_h, const T* __restrict__ q_rot, int64_t qr_stride_t,
     int64_t qr_stride_h, const float* __restrict__ cosb, const float* __restrict__ sinb, const T* __restrict__ gate,
     int64_t gate_stride_t, const T* __restrict__ cache, int n_slots, int slot, int block_size,
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const int* bt = block_table + (int64_t)tok_seq[t] * max_blocks_per_seq;
 
     // queries of this head group: [q_lat | rotary(q_rot)], rows past H are zero
-    for (int hl = warp; hl < 16; hl += 4) {
+    for (int hl = warp; hl < 16; hl += LM_NW) {
         const int h = h0 + hl;
         T* qw = Qs + hl * LD;
         if (h < H) {
@@ -222,55 +223,53 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         const int base = lo + tile * LM_KT;
         __syncthreads();                   // Ks / Ps of the previous tile are no longer read; Qs and the stats are written
         const int nkeys = min(LM_KT, pos - base + 1);
-        for (int jj = warp; jj < LM_KT; jj += 4) {
-            const bool valid = jj < nkeys;
-            const int kp = valid ? base + jj : pos;
-            const T* src = cache + (((int64_t)bt[kp / block_size] * n_slots + slot) * block_size + kp % block_size) * D;
-            const uint32_t dst = ks_a + (uint32_t)(jj * LD) * 2u;
-            for (int c = lane; c < chunks; c += 32) cp_async16(dst + c * 16, src + c * 8, valid ? 16 : 0);
+        {
+            // this warp's rows are LM_NW positions apart: walk (block, offset) instead of dividing for every row
+            int kb = (base + warp) / block_size, ko = (base + warp) - kb * block_size;
+            for (int jj = warp; jj < LM_KT; jj += LM_NW) {
+                const bool valid = jj < nkeys;
+                const T* src = valid ? cache + (((int64_t)bt[kb] * n_slots + slot) * block_size + ko) * D : cache;
+                const uint32_t dst = ks_a + (uint32_t)(jj * LD) * 2u;
+                for (int c = lane; c < chunks; c += 32) cp_async16(dst + c * 16, src + c * 8, valid ? 16 : 0);
+                ko += LM_NW;
+                while (ko >= block_size) { ko -= block_size; kb++; }
+            }
         }
         cp_async_commit();
         cp_async_wait<0>();
         __syncthreads();
 
-        // ---- S = Q K^T: this warp's key columns 8w.. and 32 + 8w..
+        // ---- S = Q K^T: this warp's key columns 8w..8w+7
         {
-            // two accumulators per key column tile (even / odd 16-wide slices of D): half the length of the dependent MMA chain
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};
+            // two accumulators (even / odd 16-wide slices of D): half the length of the dependent MMA chain; one x4 load
+            // brings the B fragments of both slices
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, u0[4] = {0.f, 0.f, 0.f, 0.f};
             const int j = lane >> 3;                                              // matrix of the x4 load this lane addresses
             const uint32_t a_addr = qs_a + (uint32_t)((lane & 15) * LD + 8 * (lane >> 4)) * 2u;
-            const uint32_t b_addr = ks_a + (uint32_t)((8 * warp + 32 * (j >> 1) + (lane & 7)) * LD + 8 * (j & 1)) * 2u;
+            const uint32_t b_row = ks_a + (uint32_t)((8 * warp + (lane & 7)) * LD + 8 * (j & 1)) * 2u;
             int kk = 0;
             for (; kk + 32 <= D; kk += 32) {
-                uint32_t a[4], c[4], b0, b1, b2, b3, d0, d1, d2, d3;
+                uint32_t a[4], c[4], b0, b1, d0, d1;
                 ldmatrix_x4(a_addr + kk * 2, a[0], a[1], a[2], a[3]);
-                ldmatrix_x4(b_addr + kk * 2, b0, b1, b2, b3);
                 ldmatrix_x4(a_addr + kk * 2 + 32, c[0], c[1], c[2], c[3]);
-                ldmatrix_x4(b_addr + kk * 2 + 32, d0, d1, d2, d3);
+                ldmatrix_x4(b_row + kk * 2 + 32 * (j >> 1), b0, b1, d0, d1);
                 mma_16816<T>(s0, a, b0, b1);
-                mma_16816<T>(s1, a, b2, b3);
                 mma_16816<T>(u0, c, d0, d1);
-                mma_16816<T>(u1, c, d2, d3);
             }
             if (kk < D) {
-                uint32_t a[4], b0, b1, b2, b3;
+                uint32_t a[4], b0, b1, d0, d1;
                 ldmatrix_x4(a_addr + kk * 2, a[0], a[1], a[2], a[3]);
-                ldmatrix_x4(b_addr + kk * 2, b0, b1, b2, b3);
+                ldmatrix_x4(b_row + kk * 2, b0, b1, d0, d1);                      // upper two matrices repeat the lower: unused
                 mma_16816<T>(s0, a, b0, b1);
-                mma_16816<T>(s1, a, b2, b3);
             }
-#pragma unroll
-            for (int e = 0; e < 4; e++) { s0[e] += u0[e]; s1[e] += u1[e]; }
             const int c0 = 8 * warp + 2 * tq;
-            Sf[g * LS + c0] = s0[0]; Sf[g * LS + c0 + 1] = s0[1];
-            Sf[(g + 8) * LS + c0] = s0[2]; Sf[(g + 8) * LS + c0 + 1] = s0[3];
-            Sf[g * LS + 32 + c0] = s1[0]; Sf[g * LS + 32 + c0 + 1] = s1[1];
-            Sf[(g + 8) * LS + 32 + c0] = s1[2]; Sf[(g + 8) * LS + 32 + c0 + 1] = s1[3];
+            Sf[g * LS + c0] = s0[0] + u0[0]; Sf[g * LS + c0 + 1] = s0[1] + u0[1];
+            Sf[(g + 8) * LS + c0] = s0[2] + u0[2]; Sf[(g + 8) * LS + c0 + 1] = s0[3] + u0[3];
         }
         __syncthreads();
 
-        // ---- online softmax: this warp's heads 4w..4w+3
-        for (int row = 4 * warp; row < 4 * warp + 4; row++) {
+        // ---- online softmax: this warp's heads 2w, 2w+1
+        for (int row = 2 * warp; row < 2 * warp + 2; row++) {
             const float x0 = lane < nkeys ? Sf[row * LS + lane] * scale : -INFINITY;
             const float x1 = lane + 32 < nkeys ? Sf[row * LS + lane + 32] * scale : -INFINITY;
             const float m_old = ms[row];
@@ -288,7 +287,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         }
         __syncthreads();
 
-        // ---- O = O * alpha + P K[:, :r]: this warp's latent column tiles w, w + 4, ...
+        // ---- O = O * alpha + P K[:, :r]: this warp's latent column tiles w, w + 8, ...
         {
             const float a_lo = al[g], a_hi = al[g + 8];
 #pragma unroll
@@ -301,7 +300,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
                 const uint32_t row_addr = ks_a + (uint32_t)((ks + 8 * (j & 1) + (lane & 7)) * LD) * 2u;
 #pragma unroll
                 for (int i = 0; i < NT; i += 2) {
-                    const int ct0 = warp + 4 * i, ct1 = warp + 4 * (i + 1);
+                    const int ct0 = warp + LM_NW * i, ct1 = warp + LM_NW * (i + 1);
                     if (ct0 >= n_col_tiles) break;
                     const int ct = (j >> 1) ? (ct1 < n_col_tiles ? ct1 : ct0) : ct0;
                     uint32_t b0, b1, b2, b3;
@@ -315,7 +314,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < NT; i++) {
-        const int ct = warp + 4 * i;
+        const int ct = warp + LM_NW * i;
         if (ct >= n_col_tiles) break;
 #pragma unroll
         for (int half = 0; half < 2; half++) {
@@ -381,7 +380,7 @@ static int launch_latent_attn_mma(const void* q_lat, int64_t ql_st, int64_t ql_s
         SLLM_REQUIRE(e == cudaSuccess, "latent_attention: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     }
     dim3 grid((unsigned)num_tokens, (unsigned)cdiv(H, 16), (unsigned)nsplit);
-    kern<<<grid, 128, smem, stream>>>(
+    kern<<<grid, LM_NW * 32, smem, stream>>>(
         (const T*)q_lat, ql_st, ql_sh, (const T*)q_rot, qr_st, qr_sh, (const float*)cosb, (const float*)sinb, (const T*)gate,
         gate_st, (const T*)cache, n_slots, slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq,
         (const int*)tok_pos, (T*)out, out_st, out_sh, H, r, dr, rot_dims, window, scale, nsplit, (float*)partial);
@@ -396,9 +395,9 @@ static int launch_latent_attn_mma(const void* q_lat, int64_t ql_st, int64_t ql_s
 
 template <typename T> struct LatentMma {
     template <typename... A> static int run(int r, A... a) {
-        if (r <= 128) return launch_latent_attn_mma<T, 4>(a...);
-        if (r <= 256) return launch_latent_attn_mma<T, 8>(a...);
-        return launch_latent_attn_mma<T, 16>(a...);
+        if (r <= 128) return launch_latent_attn_mma<T, 2>(a...);
+        if (r <= 256) return launch_latent_attn_mma<T, 4>(a...);
+        return launch_latent_attn_mma<T, 8>(a...);
     }
 };
 template <> struct LatentMma<float> {

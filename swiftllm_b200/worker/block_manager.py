@@ -69,6 +69,22 @@ class BlockManager:
             self.num_free_blocks -= total
         return new_blocks
 
+    def reserve_on_host(self, seq_ids_list, target_lens_list):
+        """Host half of allocate_blocks_for_seqs for callers that run the allocation kernel themselves (a captured CUDA graph):
+        exhaustion check + mirror update, no device work."""
+        idx = np.asarray(seq_ids_list, dtype=np.int64)
+        target = (np.asarray(target_lens_list, dtype=np.int64) + self.block_size - 1) // self.block_size
+        have = self._host_nsab[idx]
+        assert (have <= target).all()
+        if len(idx) and int(target.max()) > self.max_blocks_per_seq:
+            raise RuntimeError(f"sequence needs {int(target.max())} blocks > max_blocks_per_seq={self.max_blocks_per_seq}")
+        total = int((target - have).sum())
+        if total > self.num_free_blocks:
+            raise RuntimeError(f"No enough free blocks available on {self.device_name} ({self.num_blocks} in total, "
+                               f"{self.num_free_blocks} free, {total} requested)")
+        self._host_nsab[idx] = target
+        self.num_free_blocks -= total
+
     def check_device_status(self):
         """Debug/test helper (syncs): the allocator kernel's own error flag."""
         n, err = self._status.tolist()

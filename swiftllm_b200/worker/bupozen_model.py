@@ -64,6 +64,8 @@ class BupozenModel(PagedModelBase):
         self.last_logits = None         # fp32 logits of the rows named by forward(..., logit_rows=...)
         self.keep_residuals = False     # debugging / tests: keep the residual stream after every block of the last forward
         self.last_residuals = None
+        self._graphs = {}               # decode batch size -> captured step (EngineConfig.use_cuda_graph)
+        self._graph_pool = None
         self._init_staging()
 
     # ------------------------------------------------------------------ init
@@ -112,6 +114,7 @@ class BupozenModel(PagedModelBase):
                                               ec.block_size, device=self.device)
         # no swap space for latent rows yet: the CPU manager exists (empty) so that the shared bookkeeping paths work
         self.cpu_block_manager = BlockManager("CPU", 0, ec.max_seqs_in_block_table, 1, ec.block_size, device=self.device)
+        self._graphs = {}
 
     def swap_in_seqs(self, seq_ids_list: list):
         raise NotImplementedError("the Bupozen worker has no CPU swap space")
@@ -163,6 +166,9 @@ class BupozenModel(PagedModelBase):
         assert len(prefix_lens) == num_prefill_seqs and min(prefix_lens, default=0) >= 0
         flat_ids = list(itertools.chain(*input_ids_list))
         batch_size, num_tokens = len(input_ids_list), len(flat_ids)
+        if (getattr(self.engine_config, "use_cuda_graph", False) and num_prefill_seqs == 0 and batch_size > 0
+                and not ignore_kvcache and not logit_rows and not self.keep_residuals):
+            return self._forward_decode_graph(flat_ids, list(seq_ids_list), list(decoding_seq_lens_list))
         num_prefill_tokens = sum(prefill_lens)
         seq_lengths_list = [p + n for p, n in zip(prefix_lens, prefill_lens)] + list(decoding_seq_lens_list)
         tok_seq = [s for s, n in zip(seq_ids_list, prefill_lens) for _ in range(n)] + list(seq_ids_list[num_prefill_seqs:])
@@ -184,3 +190,72 @@ class BupozenModel(PagedModelBase):
         logits = self._forward(ids, st)
         self.last_logits = logits[batch_size:].float() if logit_rows else None
         return torch.argmax(logits[:batch_size], dim=1)
+
+    # ------------------------------------------------------------------ CUDA-graph decode path
+    def _decode_step(self, ids, seq_ids, lens, bm, caches):
+        """One pure-decode step on device-resident metadata (ids / seq_ids / lens int32 [B]): block allocation, rotary tables,
+        every layer, head, argmax.  Allocation-free apart from activations, no host sync: capturable."""
+        from swiftllm_b200.worker.kernels.block_mgmt import allocate_blocks_for_seqs as alloc_kernel
+        B = ids.shape[0]
+        alloc_kernel(bm.num_seq_allocated_blocks, bm.block_table, bm.is_block_free, seq_ids, lens, bm.block_size, None, bm._status)
+        pos = lens - 1
+        rows = torch.arange(B, dtype=torch.int32, device=self.device)
+        st = TokenInferState(batch_size=B, num_tokens=B, seq_ids=seq_ids, num_prefill_seqs=0, num_decoding_seqs=B,
+                             num_prefill_tokens=0, token_seq_ids=seq_ids, token_positions=pos, output_rows=rows,
+                             rotary=self._rotary_tables(pos))
+        saved = self.caches, self.gpu_block_manager
+        self.caches, self.gpu_block_manager = caches, bm
+        try:
+            logits = self._forward(ids, st)
+        finally:
+            self.caches, self.gpu_block_manager = saved
+        return torch.argmax(logits, dim=1)
+
+    def _forward_decode_graph(self, flat_ids, seq_ids_list, lens_list) -> torch.Tensor:
+        """Pure-decode step replayed from a CUDA graph (one graph per batch size; nothing in the step depends on the lengths
+        except through device data)."""
+        B = len(flat_ids)
+        g = self._graphs.pop(B, None)
+        if g is None:
+            cap = max(1, int(getattr(self.engine_config, "max_cuda_graphs", 16)))
+            while len(self._graphs) >= cap:
+                self._graphs.pop(next(iter(self._graphs)))
+            g = self._capture_decode_graph(B)
+        self._graphs[B] = g                      # most recently used last
+        self.gpu_block_manager.reserve_on_host(seq_ids_list, lens_list)
+        i = g["next"]; g["next"] = (i + 1) % len(g["host"])
+        host, ev = g["host"][i]
+        ev.synchronize()                         # the copy that last read this pinned buffer has finished
+        hv = host.numpy()
+        hv[:B] = flat_ids; hv[B:2 * B] = seq_ids_list; hv[2 * B:] = lens_list
+        g["meta"].copy_(host, non_blocking=True)
+        ev.record()
+        self._wait_for_swaps()
+        g["graph"].replay()
+        return g["tokens"].clone()               # the static output is overwritten by the next replay
+
+    def _capture_decode_graph(self, B: int):
+        ec, dev = self.engine_config, self.device
+        meta = torch.zeros((3 * B,), dtype=torch.int32, device=dev)
+        host = [(torch.zeros((3 * B,), dtype=torch.int32).pin_memory(), torch.cuda.Event()) for _ in range(self._STAGE_SLOTS)]
+        ids, seq_ids, lens = meta[:B], meta[B:2 * B], meta[2 * B:]
+        # warm-up (library handles, GEMM heuristics) against a scratch cache and block table: B one-token sequences
+        scratch_bm = BlockManager("scratch", B, B, 1, ec.block_size, device=dev)
+        scratch = {w: torch.zeros((B,) + tuple(c.shape[1:]), dtype=self.dtype, device=dev) for w, c in self.caches.items()}
+        seq_ids.copy_(torch.arange(B, dtype=torch.int32, device=dev))
+        lens.fill_(1)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._decode_step(ids, seq_ids, lens, scratch_bm, scratch)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        del scratch, scratch_bm
+        graph = torch.cuda.CUDAGraph()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            tokens = self._decode_step(ids, seq_ids, lens, self.gpu_block_manager, self.caches)
+        torch.cuda.synchronize()
+        return dict(graph=graph, meta=meta, host=host, next=0, tokens=tokens)

@@ -288,3 +288,33 @@ def test_bfloat16_worker_on_tensor_core_shapes():
     whole = C.run_portions(m, toks, 0, [150])[-40:]
     cut = C.run_portions(m, toks, 1, [61, 4, 64, 2, 1, 1, 17])[-40:]
     assert C.rel_err(whole, ref) < 3e-2 and C.rel_err(cut, ref) < 3e-2 and C.rel_err(cut, whole) < 2e-2
+
+
+def test_cuda_graph_decode_matches_eager():
+    """Pure-decode steps replayed from a CUDA graph (EngineConfig.use_cuda_graph) give the eager path's tokens, across block
+    borders, for two batch sizes, and leave the allocator's host mirror in step with the device."""
+    cfg = C.config([(C.mixer(heads=3, kv_rank=32, rot_dim=16, dims=16, window=11), C.DENSE),
+                    (C.mixer(heads=5, kv_rank=32, rot_dim=16, dims=16, window=6, kv_from=0), C.moe())], width=64)
+    t = O.random_tensors(cfg, seed=13)
+    t["head"] = (t["head"].float() * 4).to(t["head"].dtype)
+    prompts = [C.tokens_for(cfg, n, 70 + k) for k, n in enumerate((7, 3, 12))]
+    runs = []
+    for graph in (False, True):
+        m = C.make_worker(_make, cfg, t, dtype="bfloat16", block_size=4, num_blocks=40)
+        m.engine_config.use_cuda_graph = graph
+        last = m.forward(prompts, [0, 1, 2], [])
+        lens, toks = [len(p) for p in prompts], [list(last)]
+        for step in range(9):
+            live = [0, 1, 2] if step < 6 else [0, 2]                # the batch shrinks: a second graph
+            for i in live:
+                lens[i] += 1
+            out = m.forward([[toks[-1][i]] for i in live], live, [lens[i] for i in live])
+            nxt = list(toks[-1])
+            for i, o in zip(live, out):
+                nxt[i] = o
+            toks.append(nxt)
+        assert m.gpu_block_manager.check_device_status() >= 0
+        free = m.gpu_block_manager.num_free_blocks
+        assert free == 40 - sum((n + 3) // 4 for n in lens) and int(m.gpu_block_manager.is_block_free.sum()) == free
+        runs.append(toks)
+    assert runs[0] == runs[1]
