@@ -4,6 +4,8 @@
   python bench.py [--gpus N] [--steps K] [--warmup W]            # this implementation
   python bench.py --impl reference ...                            # CPU arm: torch-eager oracle port on host cores
   torchrun --nproc-per-node N bench.py --gpus N ...               # N > 1: tensor parallel (heads / FFN columns)
+  python bench.py --arch-compare all [--steps K] [--warmup W]     # NOT the headline: Bupozen worker beside the Llama worker
+                                                                  # (prefill / decode tok/s, attention roofline), 1 GPU
 
 Workload (BASELINE.json configs[1]): Llama-3-8B shapes, bf16, pure decode, batch 256, every sequence at
 seq_len 4096, block_size 16, synthetic seeded weights N(0, 0.02) and a KV cache pre-filled with N(0, 1).

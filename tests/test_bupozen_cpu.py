@@ -104,3 +104,16 @@ def test_long_decode(cpu):
 
 def test_greedy_generation(cpu):
     C.case_greedy_generation(cpu, C.config([(C.mixer(), C.DENSE), (C.mixer(window=5, kv_from=0), C.moe())]))
+
+
+def test_partial_library_reports_missing_kernels_loudly():
+    """A library built for one family (build(only=Worker.NATIVE_SOURCES)) binds a raising stand-in for every symbol it lacks."""
+    import swiftllm_b200
+    from swiftllm_b200 import _lib, build
+    assert set(swiftllm_b200.BupozenModel.NATIVE_SOURCES) <= set(build.sources())
+    assert swiftllm_b200.LlamaModel.NATIVE_SOURCES is None and "float32" in swiftllm_b200.BupozenModel.DTYPES \
+        and "float32" not in swiftllm_b200.LlamaModel.DTYPES
+    with pytest.raises(_lib.NativeLibraryError):
+        _lib._missing_symbol("sllm_paged_attention")(1, 2, 3)
+    with pytest.raises(AssertionError):
+        build.build(only=["no_such_file.cu"])
