@@ -243,7 +243,7 @@ int sllm_latent_kv_store(const void* dkv, int64_t row_stride, const void* norm_w
                          float eps, sllm_dtype_t dtype, sllm_stream_t stream);
 /* latent_attention: per token i at position p and head h, over the cached positions max(0, p - window + 1) .. p (all of 0 .. p
  * when window <= 0): out[i, h, :r] = sigmoid(gate[i, h]) * sum_j softmax_j((q_lat[i,h] . c_j + rotary(q_rot[i,h]) . k_rot_j) * scale) c_j.
- * q_lat / q_rot / out: element strides per token and per head; gate: [T, num_heads] logits (row stride) or NULL.  r <= 512. */
+ * q_lat / q_rot / out: element strides per token and per head; gate: [T, num_heads] logits (row stride) or NULL.  r <= 1024. */
 /* 16-bit dtypes with r % 16 == 0 and dr % 16 == 0 run on tensor cores (mma.sync over the heads of a token); other shapes and
  * SLLM_F32 run the fp32 CUDA-core kernel.  sllm_latent_attention_set_simt(1) forces the latter (returns the old setting). */
 int sllm_latent_attention_set_simt(int on);

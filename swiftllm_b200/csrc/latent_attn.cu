@@ -152,7 +152,8 @@ __global__ void __launch_bounds__(LA_MAX_HPB * 32) latent_attn_kernel(
 //   S[16, KT]  = Q[16, D] K^T          warp w: key columns 8w..8w+7, mma.m16n8k16 over D (two accumulators: even / odd slices)
 //   online softmax in fp32             warp w: heads 2w, 2w+1, two keys per lane; P rounded to 16 bits (l sums the rounded P)
 //   O[16, r]  += P[16, KT] K[:, :r]    warp w: latent columns 8(w + 8i).., B fragments by ldmatrix.trans from the same key tile
-// Needs r % 16 == 0 and dr % 16 == 0 (16-byte rows for cp.async / ldmatrix); other shapes and float storage take the kernel above.
+// Needs r % 16 == 0 and dr % 16 == 0 (16-byte rows for cp.async / ldmatrix) and a tile that fits in shared memory; other shapes and
+// float storage take the kernel above.
 constexpr int LM_KT = 64;
 constexpr int LM_NW = 8;           // warps per CTA = key column tiles per key tile (LM_KT / 8)
 
@@ -397,7 +398,8 @@ template <typename T> struct LatentMma {
     template <typename... A> static int run(int r, A... a) {
         if (r <= 128) return launch_latent_attn_mma<T, 2>(a...);
         if (r <= 256) return launch_latent_attn_mma<T, 4>(a...);
-        return launch_latent_attn_mma<T, 8>(a...);
+        if (r <= 512) return launch_latent_attn_mma<T, 8>(a...);
+        return launch_latent_attn_mma<T, 16>(a...);
     }
 };
 template <> struct LatentMma<float> {
@@ -469,8 +471,8 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
                           void* out, int64_t out_stride_t, int64_t out_stride_h, int64_t num_tokens, int num_heads, int r,
                           int dr, int rot_dims, int window, float scale, int num_splits, void* split_workspace,
                           sllm_dtype_t dtype, sllm_stream_t stream) {
-    SLLM_REQUIRE(num_tokens >= 0 && num_heads > 0 && r > 0 && r <= 512 && dr >= 0 && rot_dims >= 0 && rot_dims <= dr &&
-                 rot_dims % 2 == 0, "latent_attention: bad shape (heads %d, r %d <= 512, dr %d, rot_dims %d)", num_heads, r, dr,
+    SLLM_REQUIRE(num_tokens >= 0 && num_heads > 0 && r > 0 && r <= 1024 && dr >= 0 && rot_dims >= 0 && rot_dims <= dr &&
+                 rot_dims % 2 == 0, "latent_attention: bad shape (heads %d, r %d <= 1024, dr %d, rot_dims %d)", num_heads, r, dr,
                  rot_dims);
     SLLM_REQUIRE(n_slots > 0 && slot >= 0 && slot < n_slots && block_size > 0 && max_blocks_per_seq > 0,
                  "latent_attention: bad cache geometry");
@@ -481,7 +483,8 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
                      gate_stride_t, cache, n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out,   \
                      out_stride_t, out_stride_h, num_tokens, num_heads, r, dr, rot_dims, window, scale, (cudaStream_t)stream
     // 16-bit storage and 16-element-aligned rows: tensor cores; everything else: the fp32 CUDA-core kernel
-    const bool mma = dtype != SLLM_F32 && r % 16 == 0 && dr % 16 == 0 && !sllm_latent_attention_force_simt;
+    const size_t mma_smem = ((size_t)(16 + LM_KT) * (r + dr + 8) + 16 * (LM_KT + 8)) * 2 + (16 * (LM_KT + 1) + 48) * sizeof(float);
+    const bool mma = dtype != SLLM_F32 && r % 16 == 0 && dr % 16 == 0 && mma_smem <= 200 * 1024 && !sllm_latent_attention_force_simt;
     if (mma) {
         const int nsplit = (num_splits > 1 && split_workspace != nullptr) ? (num_splits > 64 ? 64 : num_splits) : 1;
         SLLM_DISPATCH_DTYPE_F32(dtype, return (LatentMma<T>::run(r, SLLM_LA_ARGS, nsplit, split_workspace)));
@@ -490,7 +493,8 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
         if (r <= 64) return (launch_latent_attn<T, 2>(SLLM_LA_ARGS));
         if (r <= 128) return (launch_latent_attn<T, 4>(SLLM_LA_ARGS));
         if (r <= 256) return (launch_latent_attn<T, 8>(SLLM_LA_ARGS));
-        return (launch_latent_attn<T, 16>(SLLM_LA_ARGS));
+        if (r <= 512) return (launch_latent_attn<T, 16>(SLLM_LA_ARGS));
+        return (launch_latent_attn<T, 32>(SLLM_LA_ARGS));
     });
 #undef SLLM_LA_ARGS
     return 0;

@@ -157,7 +157,8 @@ def _plain_attention(q_lat, q_rot, gate, rows, pos, window, scale, base, dims, r
     (3, 24, 6, 4, 7, 4), (11, 72, 4, 4, 33, 16), (2, 136, 8, 8, 0, 8), (9, 40, 2, 0, 32, 32),      # CUDA-core kernel
     # 16-element-aligned rows: with 16-bit storage these take the tensor-core kernel (1, 2 and 3 head groups, whole and partial
     # column tiles per warp, windows that end inside / at the edge of / beyond a 64-key tile)
-    (20, 64, 16, 16, 100, 16), (5, 128, 32, 24, 0, 8), (16, 512, 64, 64, 64, 16), (33, 208, 48, 48, 65, 4), (4, 16, 16, 0, 63, 32)])
+    (20, 64, 16, 16, 100, 16), (5, 128, 32, 24, 0, 8), (16, 512, 64, 64, 64, 16), (33, 208, 48, 48, 65, 4), (4, 16, 16, 0, 63, 32),
+    (2, 528, 16, 16, 40, 16), (3, 1000, 6, 6, 20, 8)])                                                # latents wider than 512
 def test_latent_attention_standout_keys(dtype, H, r, dr, dims, window, bs):
     """Among hundreds of small keys ONE key per query scores far above the rest, placed where an off-by-one shows: far back,
     the first and last position a window keeps, the position just outside it, both sides of a block border, position 0.  A
