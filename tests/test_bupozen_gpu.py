@@ -319,3 +319,53 @@ def test_cuda_graph_decode_matches_eager():
         assert free == 40 - sum((n + 3) // 4 for n in lens) and int(m.gpu_block_manager.is_block_free.sum()) == free
         runs.append(toks)
     assert runs[0] == runs[1]
+
+
+def test_trace_replay_command_line(tmp_path):
+    """bin/trace_run on a checkpoint folder: a mixed schedule (portions beside decoded tokens, requests that end and whose rows
+    and blocks are used again) in both dtypes, against the oracle run on each whole sequence."""
+    import json
+    import os
+    import subprocess
+    import numpy as np
+    from safetensors.torch import save_file
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = C.config([
+        (C.mixer(heads=5, dim=16, rot_dim=16, vdim=24, kv_rank=48, q_rank=40, window=21, base=5000.0, dims=16), C.moe(experts=7, top=3, ff=24)),
+        (C.mixer(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=40, q_rank=24, window=9, base=300.0, dims=6), C.DENSE),
+        (C.mixer(heads=18, dim=16, rot_dim=16, vdim=8, kv_rank=48, q_rank=40, window=33, base=5000.0, dims=16, kv_from=0), None),
+    ], width=72, vocab=131, eps=1e-6)
+    t = O.random_tensors(cfg, seed=21)
+    model_dir = tmp_path / "model"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.contiguous() for k, v in t.items()}, str(model_dir / "model.safetensors"))
+    reqs = {k: C.tokens_for(cfg, n, s) for s, (k, n) in enumerate((("a", 70), ("b", 41), ("c", 17), ("d", 5), ("e", 30)))}
+    ref = {k: O.forward(cfg, t, v).numpy() for k, v in reqs.items()}
+    plan = [[("a", 33), ("b", 2)], [("a", 31), ("b", 30), ("c", 17)], [("a", 1), ("b", 1), ("d", 5)], [("a", 1), ("b", 1), ("e", 3)],
+            [("a", 2), ("b", 7), ("e", 27)], [("a", 2)]]
+    for dtype, limit in (("float32", 2e-4), ("bfloat16", 4e-2)):
+        out = tmp_path / dtype
+        out.mkdir()
+        at, lines, rows = {k: 0 for k in reqs}, [], []
+        for n, step in enumerate(plan):
+            entries, end, rr = [], [], []
+            for k, c in step:
+                lo, hi = at[k], at[k] + c
+                entries.append({"id": k, "tokens": reqs[k][lo:hi], "want": list(range(0, c, 2))})
+                rr += [(k, p) for p in range(lo, hi, 2)]
+                at[k] = hi
+                if hi == len(reqs[k]):
+                    end.append(k)
+            lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
+            rows.append(rr)
+        # the pool is smaller than the sum of all requests: 70 + 41 + 30 live at most, rounded up per request
+        p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out", str(out),
+                            "--max-tokens", "192"], input="\n".join(lines) + "\n", capture_output=True, text=True, cwd=root)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {n}" for n in range(len(plan))]
+        for n, rr in enumerate(rows):
+            got = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(len(rr), -1)
+            for j, (k, pos) in enumerate(rr):
+                err = np.sqrt(((got[j] - ref[k][pos]) ** 2).mean() / (ref[k][pos] ** 2).mean())
+                assert err < limit, (dtype, n, k, pos, err)
