@@ -221,6 +221,9 @@ int sllm_swap_blocks_gathered(const int64_t* src_ids, const int64_t* dst_ids, in
  * out = residual / sqrt(mean(residual^2) + eps) * weight (dtype). */
 int sllm_add_rmsnorm_f32(void* residual, const void* a, const void* b, const void* weight, void* out, float eps,
                          int64_t num_tokens, int width, sllm_dtype_t dtype, sllm_stream_t stream);
+/* The same with the norm weight stored as fp32 [width] whatever dtype is (models whose norm weights stay in 32-bit). */
+int sllm_add_rmsnorm_f32w(void* residual, const void* a, const void* b, const void* weight_f32, void* out, float eps,
+                          int64_t num_tokens, int width, sllm_dtype_t dtype, sllm_stream_t stream);
 /* RMS norm of the first n columns of row-strided matrices (a slice of a fused projection): out = x / rms(x) * weight. */
 int sllm_rmsnorm_strided(const void* x, int64_t x_row_stride, const void* weight, void* out, int64_t out_row_stride,
                          float eps, int64_t num_tokens, int n, sllm_dtype_t dtype, sllm_stream_t stream);
@@ -229,6 +232,18 @@ int sllm_relu2_inplace(void* x, int64_t n, sllm_dtype_t dtype, sllm_stream_t str
 /* Mixture-of-experts router: logits fp32 [T, experts] -> weights fp32 [T, experts] = softmax over the `top` largest logits of
  * each row at their positions, 0 elsewhere.  top <= 32, experts <= 2048. */
 int sllm_moe_route(const void* logits, void* weights, int64_t num_tokens, int experts, int top, sllm_stream_t stream);
+/* Group-limited routing on scores s = softmax(logits) over ALL experts: experts form `groups` equal groups of neighbours, a
+ * group's score is its largest s, only experts of the `keep` best groups can be chosen; the `top` largest s among those are
+ * chosen (equal values: the lower index wins); weights [T, experts] fp32 = s / (sum of the chosen s + norm_eps) * scale at the
+ * chosen experts, 0 elsewhere.  groups = keep = 1: plain top-k on a full softmax. */
+int sllm_moe_route_grouped(const void* logits, void* weights, int64_t num_tokens, int experts, int top, int groups, int keep,
+                           float scale, float norm_eps, sllm_stream_t stream);
+/* Clamped gated-linear-unit experts.  u [T, 2 * cols] (dtype): per expert [gate (ff) | up (ff)], then a shared expert's
+ * [gate (shared_ff) | up (shared_ff)]; y [T, cols] (dtype), cols = experts * ff + shared_ff.  With g = min(gate, limit),
+ * v = clamp(up, -limit, limit): y = g * sigmoid(alpha * g) * (v + 1) * weights[t, e]; the shared expert uses shared_limit and
+ * weight 1.  experts or shared_ff may be 0 (weights may then be NULL / no shared part). */
+int sllm_moe_clamped_glu_scale(const void* u, const void* weights, void* y, int64_t num_tokens, int experts, int ff, float limit,
+                               int shared_ff, float shared_limit, float alpha, sllm_dtype_t dtype, sllm_stream_t stream);
 /* u [T, experts * ff] (dtype) = relu(u)^2 * weights[t, column / ff]: experts a token does not use contribute exact zeros. */
 int sllm_moe_relu2_scale_inplace(void* u, const void* weights, int64_t num_tokens, int experts, int ff, sllm_dtype_t dtype,
                                  sllm_stream_t stream);
@@ -256,6 +271,26 @@ int sllm_latent_attention(const void* q_lat, int64_t q_lat_stride_t, int64_t q_l
                           void* out, int64_t out_stride_t, int64_t out_stride_h, int64_t num_tokens, int num_heads, int r,
                           int dr, int rot_dims, int window, float scale, int num_splits, void* split_workspace,
                           sllm_dtype_t dtype, sllm_stream_t stream);
+
+/* ---- Gated sliding-window attention with grouped key/value heads over a paged cache of per-token rows
+ * [k (num_kv_heads x dk, rotary applied) | v (num_kv_heads x dv)] (new).  cache: [num_blocks, n_slots, block_size,
+ * num_kv_heads * (dk + dv)] (dtype); tok_seq / tok_pos, cosb / sinb and rot_dims as for latent attention.
+ * window_kv_store: k [T, num_kv_heads * dk] and v [T, num_kv_heads * dv] (row strides in elements) -> the tokens' cache rows. */
+int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int64_t v_row_stride, const void* cosb,
+                         const void* sinb, const void* tok_seq, const void* tok_pos, const void* block_table,
+                         int max_blocks_per_seq, void* cache, int n_slots, int slot, int block_size, int64_t num_tokens,
+                         int num_kv_heads, int dk, int dv, int rot_dims, sllm_dtype_t dtype, sllm_stream_t stream);
+/* window_attention: per token i at position p and query head h (key/value head h / (num_heads / num_kv_heads)), over the cached
+ * positions max(0, p - window + 1) .. p (all of 0 .. p when window <= 0):
+ *   out[i, h, :dv] = sigmoid(gate[i, h, :dv]) * sum_j p_j v_j,   p_j = exp(s_j) / (sink + sum_j' exp(s_j')),
+ *   s_j = rotary(q[i, h]) . k_j * scale;  sink = 1: the softmax has a value-less sink of score 0 (one more in the denominator).
+ * q [T, num_heads * dk] un-rotated, gate [T, num_heads * dv] logits or NULL, out [T, num_heads * dv]; row strides in elements.
+ * dv <= 256. */
+int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, const void* sinb, const void* gate,
+                          int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
+                          const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
+                          int64_t out_stride_t, int64_t num_tokens, int num_heads, int num_kv_heads, int dk, int dv,
+                          int rot_dims, int window, float scale, int sink, sllm_dtype_t dtype, sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

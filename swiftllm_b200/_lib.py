@@ -44,14 +44,20 @@ SIGNATURES = {
     "sllm_swap_blocks": (_I, [_P, _P, _L, _I, _P, _P, _P, _P, _L, _P]),
     "sllm_swap_blocks_gathered": (_I, [_P, _P, _L, _I, _P, _P, _P, _P, _L, _P]),
     "sllm_add_rmsnorm_f32": (_I, [_P, _P, _P, _P, _P, _F, _L, _I, _I, _P]),
+    "sllm_add_rmsnorm_f32w": (_I, [_P, _P, _P, _P, _P, _F, _L, _I, _I, _P]),
     "sllm_rmsnorm_strided": (_I, [_P, _L, _P, _P, _L, _F, _L, _I, _I, _P]),
     "sllm_relu2_inplace": (_I, [_P, _L, _I, _P]),
     "sllm_moe_route": (_I, [_P, _P, _L, _I, _I, _P]),
+    "sllm_moe_route_grouped": (_I, [_P, _P, _L, _I, _I, _I, _I, _F, _F, _P]),
+    "sllm_moe_clamped_glu_scale": (_I, [_P, _P, _P, _L, _I, _I, _F, _I, _F, _F, _I, _P]),
     "sllm_moe_relu2_scale_inplace": (_I, [_P, _P, _L, _I, _I, _I, _P]),
     "sllm_latent_kv_store": (_I, [_P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _F, _I, _P]),
     "sllm_latent_attention_set_simt": (_I, [_I]),
     "sllm_latent_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I,
                                    _I, _I, _I, _F, _I, _P, _I, _P]),
+    "sllm_window_kv_store": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _P]),
+    "sllm_window_attention": (_I, [_P, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _I, _F,
+                                   _I, _I, _P]),
 }
 
 _lib = None

@@ -9,9 +9,10 @@
 namespace sllm {
 
 // residual[t] += a[t] + b[t] (either may be null); out[t] = residual[t] / sqrt(mean(residual[t]^2) + eps) * weight
-template <typename T>
+// (WT: storage type of the weight - T, or float for models whose norm weights are kept in 32-bit)
+template <typename T, typename WT>
 __global__ void __launch_bounds__(256) add_rmsnorm_f32_kernel(float* __restrict__ residual, const T* __restrict__ a,
-                                                              const T* __restrict__ b, const T* __restrict__ weight,
+                                                              const T* __restrict__ b, const WT* __restrict__ weight,
                                                               T* __restrict__ out, float eps, int width) {
     __shared__ float red[32];
     const int64_t t = blockIdx.x;
@@ -66,6 +67,110 @@ __global__ void moe_relu2_scale_kernel(T* __restrict__ u, const float* __restric
     stf(u + i, g == 0.f ? 0.f : v * v * g);
 }
 
+// u [T, 2 * cols] holds per expert e the rows [gate_e (ff) | up_e (ff)], then the shared expert's [gate (sff) | up (sff)];
+// y [T, cols], cols = experts * ff + sff.  With g = min(gate, limit), v = clamp(up, -limit, limit):
+//     y = g * sigmoid(alpha * g) * (v + 1) * w[t, e]        (the shared expert has its own limit and weight 1)
+// so that ONE down projection over the concatenated experts yields the weighted sum of the chosen experts plus the shared one.
+template <typename T>
+__global__ void moe_clamped_glu_scale_kernel(const T* __restrict__ u, const float* __restrict__ w, T* __restrict__ y, int64_t n,
+                                             int experts, int ff, float limit, int sff, float shared_limit, float alpha) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t cols = (int64_t)experts * ff + sff;
+    const int64_t t = i / cols;
+    const int64_t c = i - t * cols;
+    const T* ur = u + t * 2 * cols;
+    float wt, lim, g, v;
+    if (c < (int64_t)experts * ff) {
+        const int e = (int)(c / ff), f = (int)(c - (int64_t)e * ff);
+        wt = w[t * experts + e];
+        if (wt == 0.f) { stf(y + i, 0.f); return; }
+        lim = limit;
+        g = ldf(ur + (int64_t)e * 2 * ff + f);
+        v = ldf(ur + (int64_t)e * 2 * ff + ff + f);
+    } else {
+        const int f = (int)(c - (int64_t)experts * ff);
+        wt = 1.f;
+        lim = shared_limit;
+        g = ldf(ur + (int64_t)experts * 2 * ff + f);
+        v = ldf(ur + (int64_t)experts * 2 * ff + sff + f);
+    }
+    g = fminf(g, lim);
+    v = fminf(fmaxf(v, -lim), lim);
+    stf(y + i, g / (1.f + expf(-alpha * g)) * (v + 1.f) * wt);
+}
+
+// One warp per token, group-limited routing on scores that are a softmax over ALL experts:
+//   s = softmax(logits);  experts form `groups` equal groups of neighbours, a group's score is its largest s, only experts of
+//   the `keep` best groups can be chosen;  the `top` largest s among those are chosen (equal values: the lower index wins);
+//   weights[t, e] = s_e / (sum of the chosen s + norm_eps) * scale at the chosen experts, 0 elsewhere.
+// Dynamic shared memory: warps * (2 * experts + groups) floats.
+__global__ void __launch_bounds__(128) moe_route_grouped_kernel(const float* __restrict__ logits, float* __restrict__ weights,
+                                                                int64_t num_tokens, int experts, int top, int groups, int keep,
+                                                                float scale, float norm_eps) {
+    extern __shared__ float vals[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= num_tokens) return;
+    float* s = vals + warp * (2 * experts + groups);      // scores
+    float* c = s + experts;                               // choice scores (-inf: may not be chosen)
+    float* gs = c + experts;                              // group scores
+    float mx = -INFINITY;
+    for (int e = lane; e < experts; e += 32) { s[e] = logits[t * experts + e]; mx = fmaxf(mx, s[e]); weights[t * experts + e] = 0.f; }
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) { s[e] = expf(s[e] - mx); sum += s[e]; }
+    sum = warp_sum(sum);
+    for (int e = lane; e < experts; e += 32) { s[e] /= sum; c[e] = -INFINITY; }
+    __syncwarp();
+    const int per = experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+        float b = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; e++) b = fmaxf(b, s[e]);
+        gs[g] = b;
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; k++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32)
+            if (gs[g] > best) { best = gs[g]; bi = g; }
+        if (best == -INFINITY) bi = 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (bi != 0x7fffffff) {
+            for (int e = bi * per + lane; e < (bi + 1) * per; e += 32) c[e] = s[e];
+            if (lane == 0) gs[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    float my_val = 0.f;            // lane k keeps the k-th choice
+    int my_idx = -1;
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32)
+            if (c[e] > best) { best = c[e]; bi = e; }
+        if (best == -INFINITY) bi = 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (lane == k && bi != 0x7fffffff) { my_val = s[bi]; my_idx = bi; }
+        __syncwarp();
+        if (lane == 0 && bi != 0x7fffffff) c[bi] = -INFINITY;
+        __syncwarp();
+    }
+    const float total = warp_sum(my_idx >= 0 ? my_val : 0.f);
+    if (my_idx >= 0) weights[t * experts + my_idx] = my_val / (total + norm_eps) * scale;
+}
+
 // One warp per token.  weights[t, e] = softmax over the `top` largest logits of row t at their experts, 0 elsewhere
 // (equal logits: the lower expert index wins).  Dynamic shared memory: warps * experts floats.
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, float* __restrict__ weights,
@@ -115,9 +220,19 @@ int sllm_add_rmsnorm_f32(void* residual, const void* a, const void* b, const voi
     SLLM_REQUIRE(num_tokens >= 0 && width > 0, "add_rmsnorm_f32: bad shape");
     if (num_tokens == 0) return 0;
     SLLM_REQUIRE(residual && weight && out, "add_rmsnorm_f32: null pointer");
-    SLLM_DISPATCH_DTYPE_F32(dtype, (add_rmsnorm_f32_kernel<T><<<(unsigned)num_tokens, 256, 0, (cudaStream_t)stream>>>(
+    SLLM_DISPATCH_DTYPE_F32(dtype, (add_rmsnorm_f32_kernel<T, T><<<(unsigned)num_tokens, 256, 0, (cudaStream_t)stream>>>(
         (float*)residual, (const T*)a, (const T*)b, (const T*)weight, (T*)out, eps, width)));
     return check_launch("add_rmsnorm_f32");
+}
+
+int sllm_add_rmsnorm_f32w(void* residual, const void* a, const void* b, const void* weight_f32, void* out, float eps,
+                          int64_t num_tokens, int width, sllm_dtype_t dtype, sllm_stream_t stream) {
+    SLLM_REQUIRE(num_tokens >= 0 && width > 0, "add_rmsnorm_f32w: bad shape");
+    if (num_tokens == 0) return 0;
+    SLLM_REQUIRE(residual && weight_f32 && out, "add_rmsnorm_f32w: null pointer");
+    SLLM_DISPATCH_DTYPE_F32(dtype, (add_rmsnorm_f32_kernel<T, float><<<(unsigned)num_tokens, 256, 0, (cudaStream_t)stream>>>(
+        (float*)residual, (const T*)a, (const T*)b, (const float*)weight_f32, (T*)out, eps, width)));
+    return check_launch("add_rmsnorm_f32w");
 }
 
 int sllm_rmsnorm_strided(const void* x, int64_t x_row_stride, const void* weight, void* out, int64_t out_row_stride,
@@ -146,6 +261,32 @@ int sllm_moe_route(const void* logits, void* weights, int64_t num_tokens, int ex
     moe_route_kernel<<<(unsigned)cdiv(num_tokens, 4), 128, 4 * experts * sizeof(float), (cudaStream_t)stream>>>(
         (const float*)logits, (float*)weights, num_tokens, experts, top);
     return check_launch("moe_route");
+}
+
+int sllm_moe_route_grouped(const void* logits, void* weights, int64_t num_tokens, int experts, int top, int groups, int keep,
+                           float scale, float norm_eps, sllm_stream_t stream) {
+    SLLM_REQUIRE(num_tokens >= 0 && experts > 0 && top > 0 && top <= experts && top <= 32 && experts <= 2048 && groups > 0 &&
+                 experts % groups == 0 && keep > 0 && keep <= groups && top <= keep * (experts / groups),
+                 "moe_route_grouped: need 0 < top <= min(32, keep * experts / groups), experts <= 2048 in equal groups "
+                 "(got top %d, experts %d, groups %d, keep %d)", top, experts, groups, keep);
+    if (num_tokens == 0) return 0;
+    SLLM_REQUIRE(logits && weights, "moe_route_grouped: null pointer");
+    moe_route_grouped_kernel<<<(unsigned)cdiv(num_tokens, 4), 128, 4 * (2 * experts + groups) * sizeof(float),
+                               (cudaStream_t)stream>>>((const float*)logits, (float*)weights, num_tokens, experts, top, groups,
+                                                       keep, scale, norm_eps);
+    return check_launch("moe_route_grouped");
+}
+
+int sllm_moe_clamped_glu_scale(const void* u, const void* weights, void* y, int64_t num_tokens, int experts, int ff, float limit,
+                               int shared_ff, float shared_limit, float alpha, sllm_dtype_t dtype, sllm_stream_t stream) {
+    SLLM_REQUIRE(num_tokens >= 0 && experts >= 0 && ff >= 0 && shared_ff >= 0 && (int64_t)experts * ff + shared_ff > 0,
+                 "moe_clamped_glu_scale: bad shape");
+    const int64_t n = num_tokens * ((int64_t)experts * ff + shared_ff);
+    if (n == 0) return 0;
+    SLLM_REQUIRE(u && y && (weights || experts == 0), "moe_clamped_glu_scale: null pointer");
+    SLLM_DISPATCH_DTYPE_F32(dtype, (moe_clamped_glu_scale_kernel<T><<<(unsigned)cdiv(n, 256), 256, 0, (cudaStream_t)stream>>>(
+        (const T*)u, (const float*)weights, (T*)y, n, experts, ff, limit, shared_ff, shared_limit, alpha)));
+    return check_launch("moe_clamped_glu_scale");
 }
 
 int sllm_moe_relu2_scale_inplace(void* u, const void* weights, int64_t num_tokens, int experts, int ff, sllm_dtype_t dtype,

@@ -86,11 +86,57 @@ class LatentAttentionSpec:
 
 
 @dataclasses.dataclass(frozen=True)
+class WindowAttentionSpec:
+    """Sizes and constants of one gated sliding-window attention mixer with grouped key/value heads: `heads` query heads share
+    `kv_heads` key/value heads (query head h uses key/value head h // (heads // kv_heads)); per head `dim` query / key entries
+    and `vdim` value entries; the softmax may have a value-less sink of score 0; the output has an element-wise sigmoid gate."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    window: int                 # a query at position p sees p - window + 1 .. p; 0 = everything up to p
+    rot_base: float
+    rot_dims: int               # leading entries of every head that turn (interleaved pairs); the rest pass through
+    scale: float
+    sink: bool = True
+    kv_from: Optional[int] = None   # every layer caches its own keys and values
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_heads * (self.dim + self.vdim)
+
+
+@dataclasses.dataclass(frozen=True)
 class FeedForwardSpec:
     kind: str                   # "dense" | "moe"
     ff: int                     # hidden size of the dense layer / of ONE expert
     experts: int = 0
     top: int = 0
+    activation: str = "relu2"   # "relu2": relu(up)^2 | "clamped_glu": min(gate, limit) * sigmoid(1.702 .) * (clamp(up) + 1)
+    limit: float = 0.0          # clamped_glu: bound of the gate (above) and of the up projection (both sides)
+    # routing.  "top_softmax": softmax over the `top` largest logits.  "softmax_grouped": scores are a softmax over all experts,
+    # only experts of the `keep` best of `groups` groups can be chosen, the chosen scores are renormalised and scaled.
+    routing: str = "top_softmax"
+    groups: int = 1
+    keep: int = 1
+    route_scale: float = 1.0
+    shared_ff: int = 0          # hidden size of a shared expert that every token uses (0: none)
+    shared_limit: float = 0.0
+
+
+def _cache_geometry(mixers):
+    """Layers that make their own cache rows own a slot; slots are grouped by row width (one cache tensor per width).
+    -> (layer -> (row width, slot within that width's tensor), row width -> number of slots)."""
+    cache_slot, slots_per_width = {}, {}
+    for i, s in enumerate(mixers):
+        if s.kv_from is None:
+            n = slots_per_width.get(s.cache_width, 0)
+            cache_slot[i] = (s.cache_width, n)
+            slots_per_width[s.cache_width] = n + 1
+    for i, s in enumerate(mixers):
+        if s.kv_from is not None:
+            cache_slot[i] = cache_slot[s.kv_from]
+    return cache_slot, slots_per_width
 
 
 class BupozenModelConfig:
@@ -98,6 +144,8 @@ class BupozenModelConfig:
     "mixer": {...}, "mlp": {...} | null}, ...]}.  Every layer is a parallel block (one RMS norm feeds the mixer and the
     feed-forward); every size may differ from layer to layer."""
     family = "bupozen"
+    embedding_scale = 1.0
+    norm_unit_offset = False    # norm weights are stored as they are applied
 
     def __init__(self, model_config: dict):
         assert model_config.get("architecture") == "Bupozen", f"not a Bupozen config: {model_config.get('architecture')!r}"
@@ -131,17 +179,7 @@ class BupozenModelConfig:
                 assert f["kind"] == "moe", f"layer {i}: unknown mlp kind {f['kind']!r}"
                 self.ffs.append(FeedForwardSpec("moe", int(f["expert"]["ff"]), int(f["router"]["experts"]), int(f["router"]["top"])))
         self.num_layers = len(self.mixers)
-        # cache geometry: layers that make their own latent own a slot; slots are grouped by row width (one tensor per width)
-        self.cache_slot = {}            # layer -> (row width, slot within that width's tensor)
-        self.cache_slots_per_width = {}
-        for i, s in enumerate(self.mixers):
-            if s.kv_from is None:
-                n = self.cache_slots_per_width.get(s.cache_width, 0)
-                self.cache_slot[i] = (s.cache_width, n)
-                self.cache_slots_per_width[s.cache_width] = n + 1
-        for i, s in enumerate(self.mixers):
-            if s.kv_from is not None:
-                self.cache_slot[i] = self.cache_slot[s.kv_from]
+        self.cache_slot, self.cache_slots_per_width = _cache_geometry(self.mixers)
 
     def get_kvslot_size(self, dtype: torch.dtype = torch.bfloat16) -> int:
         """Bytes of cache one token occupies: one [latent | rotated key part] row per layer that makes its own."""
@@ -151,3 +189,61 @@ class BupozenModelConfig:
     def load_from_model_path(model_path: str) -> "BupozenModelConfig":
         with open(os.path.join(model_path, "config.json"), "r", encoding="utf-8") as f:
             return BupozenModelConfig(json.load(f))
+
+
+# ---------------------------------------------------------------- Rivudra
+class RivudraModelConfig:
+    """config.json of the Rivudra design: {"architecture": "Rivudra", "vocab", "width", "embedding": {"scale"}, "norm": {"eps"},
+    "layers": [{"type": "attention", "mixer": {"heads", "kv_heads", "dim", "vdim", "scale", "mask": {"size"}, "rot": {"base",
+    "dims"}}, "mlp": {"kind": "moe", "router": {"experts", "top", "scale", "groups": {"count", "keep"}}, "expert": {"ff", "limit"},
+    "shared": {"ff", "limit"}} | null}, ...]}.  Every layer is a parallel block (one RMS norm, weight stored around zero and
+    applied as 1 + w, feeds the mixer and the feed-forward); every size may differ from layer to layer."""
+    family = "rivudra"
+    norm_unit_offset = True
+
+    def __init__(self, model_config: dict):
+        assert model_config.get("architecture") == "Rivudra", f"not a Rivudra config: {model_config.get('architecture')!r}"
+        self.raw = dict(model_config)
+        self.vocab_size = int(model_config["vocab"])
+        self.hidden_size = int(model_config["width"])
+        self.rms_norm_eps = float(model_config["norm"]["eps"])
+        self.embedding_scale = float((model_config.get("embedding") or {}).get("scale", 1.0))
+        self.mixers, self.ffs = [], []
+        for i, layer in enumerate(model_config["layers"]):
+            assert layer["type"] == "attention", f"layer {i}: unknown mixer type {layer['type']!r}"
+            m = layer["mixer"]
+            rot = m.get("rot") or {}
+            mask = m.get("mask") or {}
+            spec = WindowAttentionSpec(
+                heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                window=int(mask.get("size", 0)), rot_base=float(rot.get("base", 10000.0)), rot_dims=int(rot.get("dims", 0)),
+                scale=float(m["scale"]), sink=True)
+            assert spec.heads % spec.kv_heads == 0, f"layer {i}: heads must be a multiple of kv_heads"
+            assert spec.rot_dims % 2 == 0 and spec.rot_dims <= spec.dim, f"layer {i}: rot.dims must be even and <= dim"
+            self.mixers.append(spec)
+            f = layer.get("mlp")
+            if f is None:
+                self.ffs.append(None)
+                continue
+            assert f["kind"] == "moe", f"layer {i}: unknown mlp kind {f['kind']!r}"
+            r, e, sh = f["router"], f["expert"], f.get("shared")
+            groups = r.get("groups") or {}
+            ff = FeedForwardSpec(
+                "moe", int(e["ff"]), int(r["experts"]), int(r["top"]), activation="clamped_glu", limit=float(e["limit"]),
+                routing="softmax_grouped", groups=int(groups.get("count", 1)), keep=int(groups.get("keep", groups.get("count", 1))),
+                route_scale=float(r.get("scale", 1.0)), shared_ff=int(sh["ff"]) if sh else 0,
+                shared_limit=float(sh["limit"]) if sh else 0.0)
+            assert ff.experts % ff.groups == 0 and 0 < ff.keep <= ff.groups and ff.top <= ff.keep * (ff.experts // ff.groups), \
+                f"layer {i}: {ff.top} experts cannot be chosen from {ff.keep} of {ff.groups} groups of {ff.experts} experts"
+            self.ffs.append(ff)
+        self.num_layers = len(self.mixers)
+        self.cache_slot, self.cache_slots_per_width = _cache_geometry(self.mixers)
+
+    def get_kvslot_size(self, dtype: torch.dtype = torch.bfloat16) -> int:
+        """Bytes of cache one token occupies: one [keys | values] row per layer."""
+        return sum(w * n for w, n in self.cache_slots_per_width.items()) * dtype.itemsize
+
+    @staticmethod
+    def load_from_model_path(model_path: str) -> "RivudraModelConfig":
+        with open(os.path.join(model_path, "config.json"), "r", encoding="utf-8") as f:
+            return RivudraModelConfig(json.load(f))

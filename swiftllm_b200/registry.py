@@ -3,6 +3,7 @@
     family      recognised by                               config class           worker class
     llama       "model_type": "llama"                       LlamaModelConfig       worker.model.LlamaModel
     bupozen     "architecture": "Bupozen"                   BupozenModelConfig     worker.bupozen_model.BupozenModel
+    rivudra     "architecture": "Rivudra"                   RivudraModelConfig     worker.rivudra_model.RivudraModel
 
 Every worker class has the same public surface (load_weights, profile_num_blocks, init_kvcache_and_swap, forward /
 forward_async with the prefill-chunks-then-decodes batch layout, free_seqs_resources), so schedulers, examples and
@@ -20,6 +21,8 @@ _FAMILIES = {
               "swiftllm_b200.model_config:LlamaModelConfig", "swiftllm_b200.worker.model:LlamaModel"),
     "bupozen": (lambda raw: raw.get("architecture") == "Bupozen",
                 "swiftllm_b200.model_config:BupozenModelConfig", "swiftllm_b200.worker.bupozen_model:BupozenModel"),
+    "rivudra": (lambda raw: raw.get("architecture") == "Rivudra",
+                "swiftllm_b200.model_config:RivudraModelConfig", "swiftllm_b200.worker.rivudra_model:RivudraModel"),
 }
 
 

@@ -6,18 +6,24 @@ import torch
 from swiftllm_b200 import _lib
 
 
-def add_rmsnorm_f32(residual: torch.Tensor, a, b, weight: torch.Tensor, eps: float, out: torch.Tensor = None) -> torch.Tensor:
+def add_rmsnorm_f32(residual: torch.Tensor, a, b, weight: torch.Tensor, eps: float, out: torch.Tensor = None,
+                    out_dtype: torch.dtype = None) -> torch.Tensor:
     """residual (fp32 [T, W], updated in place) += a + b (either may be None); returns rmsnorm(residual) * weight in
-    weight's dtype."""
+    `out_dtype` (default: weight's dtype).  The weight is stored in the output dtype or in fp32."""
     assert residual.dtype == torch.float32 and residual.is_contiguous() and weight.is_contiguous()
     _lib.require_device(residual)
     T, W = residual.shape
     if out is None:
-        out = torch.empty((T, W), dtype=weight.dtype, device=residual.device)
+        out = torch.empty((T, W), dtype=out_dtype or weight.dtype, device=residual.device)
     for x in (a, b):
-        assert x is None or (x.dtype == weight.dtype and x.is_contiguous() and x.shape == residual.shape)
-    _lib.check(_lib.lib().sllm_add_rmsnorm_f32(residual.data_ptr(), _lib.ptr(a), _lib.ptr(b), weight.data_ptr(), out.data_ptr(),
-                                               eps, T, W, _lib.dtype_tag_f32(weight.dtype), _lib.stream()), "add_rmsnorm_f32")
+        assert x is None or (x.dtype == out.dtype and x.is_contiguous() and x.shape == residual.shape)
+    if weight.dtype == out.dtype:
+        fn, what = _lib.lib().sllm_add_rmsnorm_f32, "add_rmsnorm_f32"
+    else:
+        assert weight.dtype == torch.float32, "norm weights are stored in the activation dtype or in float32"
+        fn, what = _lib.lib().sllm_add_rmsnorm_f32w, "add_rmsnorm_f32w"
+    _lib.check(fn(residual.data_ptr(), _lib.ptr(a), _lib.ptr(b), weight.data_ptr(), out.data_ptr(), eps, T, W,
+                  _lib.dtype_tag_f32(out.dtype), _lib.stream()), what)
     return out
 
 
@@ -57,3 +63,31 @@ def moe_relu2_scale_inplace(u: torch.Tensor, weights: torch.Tensor, ff: int):
     assert u.shape == (T, E * ff)
     _lib.check(_lib.lib().sllm_moe_relu2_scale_inplace(u.data_ptr(), weights.data_ptr(), T, E, ff, _lib.dtype_tag_f32(u.dtype),
                                                        _lib.stream()), "moe_relu2_scale_inplace")
+
+
+def moe_route_grouped(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float, norm_eps: float) -> torch.Tensor:
+    """logits fp32 [T, E] -> routing weights fp32 [T, E]: scores are a softmax over all experts; only experts of the `keep`
+    best of `groups` equal groups (a group's score: its largest score) can be chosen; the `top` largest of those get
+    score / (sum of chosen scores + norm_eps) * scale, the others 0."""
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    _lib.require_device(logits)
+    w = torch.empty_like(logits)
+    _lib.check(_lib.lib().sllm_moe_route_grouped(logits.data_ptr(), w.data_ptr(), logits.shape[0], logits.shape[1], top, groups,
+                                                 keep, scale, norm_eps, _lib.stream()), "moe_route_grouped")
+    return w
+
+
+def moe_clamped_glu_scale(u: torch.Tensor, weights, experts: int, ff: int, limit: float, shared_ff: int, shared_limit: float,
+                          alpha: float) -> torch.Tensor:
+    """u [T, 2 * (experts * ff + shared_ff)]: per expert [gate | up], then the shared expert's [gate | up] ->
+    y [T, experts * ff + shared_ff] = min(gate, limit) * sigmoid(alpha * .) * (clamp(up, +-limit) + 1) * weights[t, expert]
+    (the shared expert: its own limit, weight 1)."""
+    assert u.is_contiguous() and (weights is None or (weights.dtype == torch.float32 and weights.is_contiguous()))
+    _lib.require_device(u)
+    T, cols = u.shape[0], experts * ff + shared_ff
+    assert u.shape == (T, 2 * cols) and (experts == 0 or weights.shape == (T, experts))
+    y = torch.empty((T, cols), dtype=u.dtype, device=u.device)
+    _lib.check(_lib.lib().sllm_moe_clamped_glu_scale(u.data_ptr(), _lib.ptr(weights), y.data_ptr(), T, experts, ff, limit, shared_ff,
+                                                     shared_limit, alpha, _lib.dtype_tag_f32(u.dtype), _lib.stream()),
+               "moe_clamped_glu_scale")
+    return y

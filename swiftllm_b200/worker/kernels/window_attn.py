@@ -1,0 +1,39 @@
+"""Gated sliding-window attention with grouped key/value heads over the paged cache (csrc/window_attn.cu).  Cache layout
+[num_blocks, slots, block_size, G * (dk + dv)]: per token and layer ONE row [rotated keys of all G heads | their values]."""
+import torch
+
+from swiftllm_b200 import _lib
+
+
+def _stride0(x: torch.Tensor) -> int:
+    return x.stride(0) if x.shape[0] > 1 else max(x.stride(0), x.shape[1])
+
+
+def window_kv_store(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, slot: int, block_table: torch.Tensor, infer_state,
+                    kv_heads: int, dk: int, dv: int, rot_dims: int, cos: torch.Tensor, sin: torch.Tensor):
+    """k [T, G * dk], v [T, G * dv] (row-strided slices are fine): rotate the keys, write the tokens' cache rows."""
+    T = k.shape[0]
+    assert k.dim() == 2 and k.stride(1) == 1 and v.stride(1) == 1 and k.shape[1] == kv_heads * dk and v.shape == (T, kv_heads * dv)
+    assert cache.is_contiguous() and cache.dtype == k.dtype == v.dtype and cache.shape[3] == kv_heads * (dk + dv)
+    _lib.require_device(k)
+    _lib.check(_lib.lib().sllm_window_kv_store(
+        k.data_ptr(), _stride0(k), v.data_ptr(), _stride0(v), _lib.ptr(cos), _lib.ptr(sin), infer_state.token_seq_ids.data_ptr(),
+        infer_state.token_positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], cache.data_ptr(), cache.shape[1],
+        slot, cache.shape[2], T, kv_heads, dk, dv, rot_dims, _lib.dtype_tag_f32(k.dtype), _lib.stream()), "window_kv_store")
+
+
+def window_attention(q: torch.Tensor, gate, cache: torch.Tensor, slot: int, block_table: torch.Tensor, infer_state,
+                     out: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, rot_dims: int, window: int, scale: float,
+                     sink: bool, cos: torch.Tensor, sin: torch.Tensor):
+    """q [T, H * dk] (un-rotated), gate [T, H * dv] logits or None, out [T, H * dv]; row-strided slices are fine."""
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape == (T, heads * dk) and out.shape == (T, heads * dv)
+    assert gate is None or (gate.shape == (T, heads * dv) and gate.stride(1) == 1 and gate.dtype == q.dtype)
+    assert cache.shape[3] == kv_heads * (dk + dv) and cache.dtype == q.dtype == out.dtype
+    _lib.require_device(q)
+    _lib.check(_lib.lib().sllm_window_attention(
+        q.data_ptr(), _stride0(q), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(gate), _stride0(gate) if gate is not None else 0,
+        cache.data_ptr(), cache.shape[1], slot, cache.shape[2], block_table.data_ptr(), block_table.shape[1],
+        infer_state.token_seq_ids.data_ptr(), infer_state.token_positions.data_ptr(), out.data_ptr(), _stride0(out), T, heads,
+        kv_heads, dk, dv, rot_dims, window, scale, 1 if sink else 0, _lib.dtype_tag_f32(q.dtype), _lib.stream()),
+        "window_attention")

@@ -1,4 +1,5 @@
-"""Feed-forward sublayers with the squared-ReLU activation: a dense one and a mixture of experts.
+"""Feed-forward sublayers: dense and mixture-of-experts with the squared-ReLU activation, and a mixture of clamped
+gated-linear-unit experts with group-limited routing and a shared expert.
 
 Mixture of experts.  Router logits are an fp32 GEMM; `moe_route` turns them into a [T, experts] weight matrix (softmax over the
 `top` largest logits at their experts, exact zeros elsewhere).  The experts' up projections are ONE GEMM over the row-wise
@@ -10,7 +11,11 @@ tokens * top >= experts)."""
 import torch
 
 from swiftllm_b200.worker.kernels.linear import linear
-from swiftllm_b200.worker.kernels.parallel_block import moe_relu2_scale_inplace, moe_route, relu2_inplace
+from swiftllm_b200.worker.kernels.parallel_block import (moe_clamped_glu_scale, moe_relu2_scale_inplace, moe_route,
+                                                         moe_route_grouped, relu2_inplace)
+
+GLU_SIGMOID_SLOPE = 1.702       # the gate's activation is g * sigmoid(1.702 g)
+ROUTE_NORM_EPS = 1e-20          # added to the sum of the chosen scores before dividing by it
 
 
 class Relu2FeedForward:
@@ -36,7 +41,28 @@ class Relu2MixtureOfExperts:
         return linear(u, w.down)
 
 
+class ClampedGluMixtureOfExperts:
+    """Experts y = min(gate, limit) * sigmoid(1.702 .) * (clamp(up, +-limit) + 1) -> down.  Same dense formulation as above:
+    ONE [gate | up] GEMM over all experts AND the shared expert (its rows come last), the activation kernel applies the routing
+    weight (1 for the shared expert), ONE down GEMM sums everything.  Routing: softmax over all experts, group-limited top-k,
+    chosen scores renormalised and scaled (fp32)."""
+
+    def __init__(self, spec, weight):
+        self.spec, self.weight = spec, weight
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        f, w = self.spec, self.weight
+        logits = linear(h.float(), w.router)                    # fp32 GEMM (TF32 stays off)
+        weights = moe_route_grouped(logits, f.top, f.groups, f.keep, f.route_scale, ROUTE_NORM_EPS)
+        u = linear(h, w.up)                                     # [T, 2 * (experts * ff + shared_ff)]
+        y = moe_clamped_glu_scale(u, weights, f.experts, f.ff, f.limit, f.shared_ff, f.shared_limit, GLU_SIGMOID_SLOPE)
+        return linear(y, w.down)
+
+
 def build_feed_forward(spec, weight):
     if spec is None:
         return None
+    if spec.activation == "clamped_glu":
+        assert spec.kind == "moe" and spec.routing == "softmax_grouped"
+        return ClampedGluMixtureOfExperts(spec, weight)
     return (Relu2FeedForward if spec.kind == "dense" else Relu2MixtureOfExperts)(spec, weight)

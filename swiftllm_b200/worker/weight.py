@@ -159,6 +159,66 @@ def load_bupozen_weights(model_config, dtype: torch.dtype, model_path: Optional[
     return weight
 
 
+class RivudraLayerWeight:
+    """One parallel block.  Checkpoint names: `l<i>.norm1`, `l<i>.mix.{q, k, v, g, o}`, `l<i>.mlp.{router, e<k>.{gate, up, down},
+    shared.{gate, up, down}}`.  Fusions made at load time: `in_proj` = [q ; k ; v ; g] (one GEMM on the block's normed input);
+    `up` = per expert [gate ; up], then the shared expert's [gate ; up]; `down` = the experts' and the shared expert's down
+    projections side by side.  Norm weights are stored around zero and applied as 1 + w: kept as fp32 (1 + w)."""
+
+    def __init__(self, layer_id: int, model_config, dtype: torch.dtype):
+        self.layer_id, self.model_config, self.dtype = layer_id, model_config, dtype
+
+    def load_weights(self, getter: Callable, device):
+        c, i = self.model_config, self.layer_id
+        m, f, W = c.mixers[i], c.ffs[i], c.hidden_size
+
+        def get(name, shape, dtype=None):
+            w = getter(f"l{i}.{name}", shape, dtype or self.dtype)
+            assert isinstance(w, torch.Tensor) and tuple(w.shape) == tuple(shape), f"l{i}.{name}: expected shape {tuple(shape)}"
+            return w.to(device=device, dtype=dtype or self.dtype).contiguous()
+
+        self.norm = unit_offset_norm(get("norm1", (W,), torch.float32))
+        self.in_proj = torch.cat([get("mix.q", (m.heads * m.dim, W)), get("mix.k", (m.kv_heads * m.dim, W)),
+                                  get("mix.v", (m.kv_heads * m.vdim, W)), get("mix.g", (m.heads * m.vdim, W))], dim=0).contiguous()
+        self.o = get("mix.o", (W, m.heads * m.vdim))
+        if f is None:
+            return
+        self.router = get("mlp.router", (f.experts, W), torch.float32)                                # the router runs in fp32
+        names = [(f"mlp.e{e}", f.ff) for e in range(f.experts)] + ([("mlp.shared", f.shared_ff)] if f.shared_ff else [])
+        self.up = torch.cat([get(f"{n}.{part}", (ff, W)) for n, ff in names for part in ("gate", "up")], dim=0).contiguous()
+        self.down = torch.cat([get(f"{n}.down", (W, ff)) for n, ff in names], dim=1).contiguous()
+
+
+def unit_offset_norm(w: torch.Tensor) -> torch.Tensor:
+    """A norm weight stored around zero -> the fp32 factor 1 + w it is applied as."""
+    return (w.float() + 1.0).contiguous()
+
+
+class RivudraWeight:
+    def __init__(self, model_config, dtype: torch.dtype):
+        self.model_config, self.dtype = model_config, dtype
+        self.layers = [RivudraLayerWeight(i, model_config, dtype) for i in range(model_config.num_layers)]
+
+    def load_weights(self, getter: Callable, device="cuda"):
+        c = self.model_config
+        vs = (c.vocab_size, c.hidden_size)
+        self.wte = getter("embed", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.final_norm = unit_offset_norm(getter("final.norm", (c.hidden_size,), torch.float32).to(device=device))
+        self.lm_head = getter("head", vs, self.dtype).to(device=device, dtype=self.dtype).contiguous()
+        self.lm_head_sharded = False
+        for layer in self.layers:
+            layer.load_weights(getter, device)
+
+
+def load_rivudra_weights(model_config, dtype: torch.dtype, model_path: Optional[str], use_dummy: bool = False,
+                         getter: Optional[Callable] = None, device="cuda") -> RivudraWeight:
+    if getter is None:
+        getter = dummy_getter(device) if use_dummy else checkpoint_getter(model_path, device)
+    weight = RivudraWeight(model_config, dtype)
+    weight.load_weights(getter, device)
+    return weight
+
+
 # ---------------------------------------------------------------- getters
 def dummy_getter(device="cuda"):
     """weight.py:215-218: uniform(-1e-3, 1e-3), unseeded ("mainly for profiling")."""
