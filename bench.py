@@ -4,7 +4,7 @@
   python bench.py [--gpus N] [--steps K] [--warmup W]            # this implementation
   python bench.py --impl reference ...                            # CPU arm: torch-eager oracle port on host cores
   torchrun --nproc-per-node N bench.py --gpus N ...               # N > 1: tensor parallel (heads / FFN columns)
-  python bench.py --arch-compare all [--steps K] [--warmup W]     # NOT the headline: Bupozen worker beside the Llama worker
+  python bench.py --arch-compare all [--steps K] [--warmup W]     # NOT the headline: Bupozen / Rivudra workers beside the Llama worker
                                                                   # (prefill / decode tok/s, attention roofline), 1 GPU
 
 Workload (BASELINE.json configs[1]): Llama-3-8B shapes, bf16, pure decode, batch 256, every sequence at
@@ -87,9 +87,11 @@ def parse():
     ap.add_argument("--parity-seqs", type=int, default=2, help="sequences re-run through the CPU oracle (tokens + logits)")
     ap.add_argument("--no-live-traffic", action="store_true", help="skip the ncu DRAM-byte measurement of the decode kernel")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--arch-models", type=str, default="", metavar="NAMES",
+                    help="with --arch-compare: only these workers (comma-separated: bupozen, rivudra, llama); default all")
     ap.add_argument("--arch-compare", type=str, default="", metavar="SIZES",
-                    help="instead of the headline workload: prefill and decode throughput of the Bupozen worker beside the Llama "
-                         "worker at equal width / depth (random weights), with the attention kernels' roofline fractions; "
+                    help="instead of the headline workload: prefill and decode throughput of the Bupozen and Rivudra workers beside the "
+                         "Llama worker at equal width / depth (random weights), with the attention kernels' roofline fractions; "
                          "comma-separated sizes out of " + ",".join(ARCH_SIZES) + " or 'all'.  One JSON line per size and model.")
     ap.add_argument("--cpu-sample-seqs", type=int, default=8)
     ap.add_argument("--profile-range", type=int, default=0,
@@ -107,8 +109,9 @@ ARCH_SIZES = {
 }
 
 
-def _arch_models(sz, dtype):
-    """(name, worker) pairs: Bupozen (layers alternate own-latent + dense ff / borrowed latent + MoE) and the closest existing
+def _arch_models(sz, dtype, only=None):
+    """(name, worker) pairs: Rivudra (gated sliding-window GQA attention with heads / 4 KV heads, every layer a mixture of experts
+    with a shared expert), Bupozen (layers alternate own-latent + dense ff / borrowed latent + MoE) and the closest existing
     family, Llama with GQA (heads / 4 KV heads) and a gated ff of the same hidden size, same width / depth / vocabulary."""
     import swiftllm_b200
     from swiftllm_b200 import registry
@@ -127,12 +130,23 @@ def _arch_models(sz, dtype):
     llama = dict(model_type="llama", num_hidden_layers=sz["layers"], num_attention_heads=H, num_key_value_heads=max(1, H // 4),
                  hidden_size=W, intermediate_size=sz["ff"], vocab_size=sz["vocab"], max_position_embeddings=8192,
                  rope_theta=10000.0, rms_norm_eps=1e-5, hidden_act="silu", rope_scaling=None)
-    for name, raw in (("bupozen", bup), ("llama", llama)):
+    G = max(1, H // 4)
+    riv_layers = [{"type": "attention",
+                   "mixer": {"heads": H, "kv_heads": G, "dim": W // H, "vdim": W // H, "mask": {"size": sz["window"]},
+                             "rot": {"base": 10000.0, "dims": W // H // 2}, "scale": (W // H) ** -0.5},
+                   "mlp": {"kind": "moe", "expert": {"ff": sz["eff"], "limit": 7.0}, "shared": {"ff": sz["eff"], "limit": 7.0},
+                           "router": {"experts": sz["experts"], "top": sz["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}}}}
+                  for _ in range(sz["layers"])]
+    riv = {"architecture": "Rivudra", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+           "layers": riv_layers}
+    for name, raw in (("bupozen", bup), ("rivudra", riv), ("llama", llama)):
+        if only and name not in only:
+            continue
         ec = swiftllm_b200.EngineConfig(model_path="", use_dummy=False, block_size=16, gpu_mem_utilization=0.9, num_cpu_blocks=0,
                                         max_seqs_in_block_table=128, max_blocks_per_seq=512, max_batch_size=64,
                                         max_tokens_in_batch=16384, dtype=dtype)
         model = registry.create_model(ec, registry.model_config_from_dict(raw))
-        model.load_weights(synthetic_getter(seed=0, std=0.02, device="cuda"))
+        model.load_weights(synthetic_getter(seed=0, std=0.02, device="cuda", norm_offset=0.0 if name == "rivudra" else 1.0))
         model.init_kvcache_and_swap(64 * 4096 // 16 + 64)
         yield name, raw, model
         del model
@@ -179,11 +193,13 @@ def run_arch_compare(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")           # > L2: written between timed iterations
     for size in names:
         sz = ARCH_SIZES[size]
-        for name, raw, model in _arch_models(sz, "bfloat16"):
+        for name, raw, model in _arch_models(sz, "bfloat16", only=[m for m in args.arch_models.split(",") if m]):
             g = torch.Generator().manual_seed(0)
             prompts = [torch.randint(0, sz["vocab"], (prompt_len,), generator=g).tolist() for _ in range(n_prompts)]
             if name == "bupozen":
                 mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.latent_attention"), ["latent_attention"]
+            elif name == "rivudra":
+                mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.window_attention"), ["window_attention"]
             else:
                 mod, attrs = importlib.import_module("swiftllm_b200.worker.layers.transformer_layer"), ["prefill_attention", "paged_attention"]
 
@@ -239,6 +255,14 @@ def run_arch_compare(args):
                 vis_dec = dec_batch * min(ctx + 1, Wn)
                 fl_dec = L * vis_dec * H * (4 * r + 2 * dr)
                 by_dec = L * vis_dec * (r + dr) * 2
+            elif name == "rivudra":
+                D, nkv, Wn = sz["width"] // H, max(1, H // 4), sz["window"]
+                vis_pre = sum(min(p + 1, Wn) for p in range(prompt_len)) * n_prompts
+                fl_pre = L * vis_pre * H * D * 4
+                by_pre = L * n_prompts * prompt_len * (3 * H + 2 * nkv) * D * 2          # q, gate, out + the K / V rows once
+                vis_dec = dec_batch * min(ctx + 1, Wn)
+                fl_dec = L * vis_dec * H * D * 4
+                by_dec = L * vis_dec * 2 * nkv * D * 2
             else:
                 D, nkv = sz["width"] // H, max(1, H // 4)
                 fl_pre = L * n_prompts * (prompt_len * (prompt_len + 1) // 2) * H * D * 4

@@ -227,8 +227,9 @@ def dummy_getter(device="cuda"):
     return get
 
 
-def synthetic_getter(seed: int = 0, std: float = 0.02, device="cuda"):
-    """Seeded synthetic weights of realistic scale: N(0, std) projections, 1 + N(0, std) norms.
+def synthetic_getter(seed: int = 0, std: float = 0.02, device="cuda", norm_offset: float = 1.0):
+    """Seeded synthetic weights of realistic scale: N(0, std) projections, norm_offset + N(0, std) norms
+    (0 for designs that store norm weights around zero).
     Deterministic per tensor key, so every TP rank generates the same full tensor before slicing."""
     import zlib
 
@@ -237,7 +238,7 @@ def synthetic_getter(seed: int = 0, std: float = 0.02, device="cuda"):
         g.manual_seed((seed * 1000003 + zlib.crc32(key.encode())) & 0x7FFFFFFF)
         t = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std
         if key.endswith(("norm.weight", "layernorm.weight", ".norm", ".norm1")):
-            t += 1.0
+            t += norm_offset
         return t.to(dtype)
     return get
 

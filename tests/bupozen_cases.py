@@ -9,6 +9,14 @@ import numpy as np
 import torch
 
 from oracle import bupozen as O
+from oracle import rivudra as _rivudra
+
+_ORACLES = {"Bupozen": O, "Rivudra": _rivudra}
+
+
+def oracle_of(cfg):
+    """The plain restatement of the design a configuration names (the scenarios below serve every parallel-block design)."""
+    return _ORACLES[cfg["architecture"]]
 
 
 def mixer(heads=3, dim=8, rot_dim=6, vdim=5, kv_rank=24, q_rank=12, window=7, base=100.0, dims=4, kv_from=None):
@@ -88,10 +96,10 @@ TOL = 2e-4     # fp32 worker against the fp32 oracle: relative rms error of the 
 
 # ---------------------------------------------------------------- scenarios
 def case_whole_prompt(make, cfg, n=23, seed=0):
-    t = O.random_tensors(cfg, seed=seed)
+    t = oracle_of(cfg).random_tensors(cfg, seed=seed)
     model = make_worker(make, cfg, t)
     toks = tokens_for(cfg, n, seed)
-    ref, layers = O.forward(cfg, t, toks, keep_layers=True)
+    ref, layers = oracle_of(cfg).forward(cfg, t, toks, keep_layers=True)
     model.keep_residuals = True
     got = run_portions(model, toks, 1, [n])
     for i, r in enumerate(model.last_residuals):
@@ -101,10 +109,10 @@ def case_whole_prompt(make, cfg, n=23, seed=0):
 
 def case_prefill_vs_decode(make, cfg, n=30, first=3, seed=1):
     """The first tokens as one portion, every other token decoded alone (windows slide past their start while decoding)."""
-    t = O.random_tensors(cfg, seed=seed)
+    t = oracle_of(cfg).random_tensors(cfg, seed=seed)
     model = make_worker(make, cfg, t)
     toks = tokens_for(cfg, n, seed)
-    ref = O.forward(cfg, t, toks)
+    ref = oracle_of(cfg).forward(cfg, t, toks)
     got = run_portions(model, toks, 2, [first] + [1] * (n - first))
     assert rel_err(got, ref) < TOL
     # token by token from the very first one (position 0 alone is a one-token prompt)
@@ -114,9 +122,9 @@ def case_prefill_vs_decode(make, cfg, n=30, first=3, seed=1):
 
 
 def case_portions(make, cfg, seed=2):
-    t = O.random_tensors(cfg, seed=seed)
+    t = oracle_of(cfg).random_tensors(cfg, seed=seed)
     toks = tokens_for(cfg, 37, seed)
-    ref = O.forward(cfg, t, toks)
+    ref = oracle_of(cfg).forward(cfg, t, toks)
     model = make_worker(make, cfg, t)
     for cuts in ([2, 2, 2, 31], [5, 7, 1, 3, 2, 19], [36, 1], [4] * 9 + [1], [13, 2, 22]):
         got = run_portions(model, toks, 0, cuts)
@@ -129,10 +137,10 @@ def case_portions(make, cfg, seed=2):
 
 def case_mixed_batch(make, cfg, seed=3):
     """Unequal requests in one batch - portions of some beside decoded tokens of others - against each alone."""
-    t = O.random_tensors(cfg, seed=seed)
+    t = oracle_of(cfg).random_tensors(cfg, seed=seed)
     lens = [19, 6, 31, 1]
     seqs = [tokens_for(cfg, n, seed * 10 + k) for k, n in enumerate(lens)]
-    refs = [O.forward(cfg, t, s) for s in seqs]
+    refs = [oracle_of(cfg).forward(cfg, t, s) for s in seqs]
     model = make_worker(make, cfg, t)
     rows = [3, 0, 2, 1]
     got = [[None] * n for n in lens]
@@ -164,10 +172,10 @@ def case_mixed_batch(make, cfg, seed=3):
 def case_blocks_and_rows_reused(make, cfg, seed=4):
     """A pool that only fits the live requests: blocks and block-table rows of finished requests are handed out again, in
     another order, while they still hold the old rows."""
-    t = O.random_tensors(cfg, seed=seed)
+    t = oracle_of(cfg).random_tensors(cfg, seed=seed)
     model = make_worker(make, cfg, t, block_size=4, num_blocks=12, rows=2)
     a, b, c = tokens_for(cfg, 22, 40), tokens_for(cfg, 17, 41), tokens_for(cfg, 26, 42)
-    ra, rb, rc = (O.forward(cfg, t, s) for s in (a, b, c))
+    ra, rb, rc = (oracle_of(cfg).forward(cfg, t, s) for s in (a, b, c))
     ga = run_portions(model, a, 0, [10, 12])                 # 6 blocks
     gb = run_portions(model, b, 1, [17])                     # 5 blocks: 1 left
     assert model.gpu_block_manager.num_free_blocks == 1
@@ -181,9 +189,9 @@ def case_blocks_and_rows_reused(make, cfg, seed=4):
 
 
 def case_long_decode(make, cfg, seed=5, n=60):
-    t = O.random_tensors(cfg, seed=seed)
+    t = oracle_of(cfg).random_tensors(cfg, seed=seed)
     toks = tokens_for(cfg, n, seed)
-    ref = O.forward(cfg, t, toks)
+    ref = oracle_of(cfg).forward(cfg, t, toks)
     model = make_worker(make, cfg, t, block_size=8, num_blocks=8)
     got = run_portions(model, toks, 3, [2] + [1] * (n - 2))
     assert rel_err(got, ref) < TOL
@@ -193,7 +201,7 @@ def case_long_decode(make, cfg, seed=5, n=60):
 def oracle_greedy(cfg, t, prompt, new_tokens):
     toks, out = list(prompt), []
     for _ in range(new_tokens):
-        nxt = int(torch.argmax(O.forward(cfg, t, toks)[-1]))
+        nxt = int(torch.argmax(oracle_of(cfg).forward(cfg, t, toks)[-1]))
         out.append(nxt); toks.append(nxt)
     return out
 
@@ -202,7 +210,7 @@ def case_greedy_generation(make, cfg, seed=6):
     """Through the worker's scheduler loop (worker/chunking.py: prompts in portions beside running decodes)."""
     from swiftllm_b200.worker.chunking import run_greedy
     # sharpen the head so that greedy choices do not hinge on rounding
-    t = O.random_tensors(cfg, seed=seed)
+    t = oracle_of(cfg).random_tensors(cfg, seed=seed)
     t["head"] = (t["head"].float() * 4).to(t["head"].dtype)
     prompts = [tokens_for(cfg, n, 60 + k) for k, n in enumerate((11, 3, 17))]
     model = make_worker(make, cfg, t, block_size=4, num_blocks=30, rows=4)

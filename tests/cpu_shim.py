@@ -132,13 +132,14 @@ def _swap_blocks(src_ids, dst_ids, is_swap_in, k_cache, v_cache, k_swap, v_swap)
 
 # ---------------------------------------------------------------- stand-ins of the parallel-block / latent-attention kernels
 # (restated from the kernels' contracts in include/swiftllm_b200.h; fp32 arithmetic, results rounded to the storage dtype)
-def _add_rmsnorm_f32(residual, a, b, weight, eps, out=None):
+def _add_rmsnorm_f32(residual, a, b, weight, eps, out=None, out_dtype=None):
     if a is not None or b is not None:
         y = a.float() if a is not None else torch.zeros_like(residual)
         if b is not None:
             y = y + b.float()
         residual += y
-    o = (residual / torch.sqrt((residual * residual).mean(-1, keepdim=True) + eps) * weight.float()).to(weight.dtype)
+    o = (residual / torch.sqrt((residual * residual).mean(-1, keepdim=True) + eps) * weight.float()).to(
+        out.dtype if out is not None else (out_dtype or weight.dtype))
     if out is None:
         return o
     out.copy_(o)
@@ -205,6 +206,59 @@ def _latent_attention(q_lat, q_rot, gate, cache, slot, block_table, st, out, rot
         out[t] = o.to(out.dtype)
 
 
+def _moe_route_grouped(logits, top, groups, keep, scale, norm_eps):
+    s = torch.softmax(logits, dim=-1)
+    T, E = s.shape
+    gbest = s.view(T, groups, E // groups).max(-1).values
+    kept = torch.zeros(T, groups, dtype=torch.bool).scatter_(1, torch.topk(gbest, keep, dim=-1).indices, True)
+    choice = s.masked_fill(~kept.repeat_interleave(E // groups, dim=1), float("-inf"))
+    idx = torch.topk(choice, top, dim=-1).indices
+    w = s.gather(1, idx)
+    return torch.zeros_like(s).scatter_(1, idx, w / (w.sum(-1, keepdim=True) + norm_eps) * scale)
+
+
+def _moe_clamped_glu_scale(u, weights, experts, ff, limit, shared_ff, shared_limit, alpha):
+    T = u.shape[0]
+    uf = u.float()
+
+    def act(block, n, lim):
+        g, v = block[..., :n].clamp(max=lim), block[..., n:].clamp(-lim, lim)
+        return g * torch.sigmoid(alpha * g) * (v + 1.0)
+    parts = []
+    if experts:
+        parts.append((act(uf[:, :2 * experts * ff].view(T, experts, 2 * ff), ff, limit) * weights[:, :, None]).reshape(T, experts * ff))
+    if shared_ff:
+        parts.append(act(uf[:, 2 * experts * ff:], shared_ff, shared_limit))
+    return torch.cat(parts, dim=1).to(u.dtype)
+
+
+def _window_kv_store(k, v, cache, slot, block_table, st, kv_heads, dk, dv, rot_dims, cos, sin):
+    T = k.shape[0]
+    kr = _rot_pairs(k.float().view(T, kv_heads, dk), cos, sin, rot_dims).reshape(T, kv_heads * dk).to(k.dtype)
+    bs = cache.shape[2]
+    for t, (sq, p) in enumerate(zip(st.token_seq_ids.tolist(), st.token_positions.tolist())):
+        cache[int(block_table[sq, p // bs]), slot, p % bs] = torch.cat([kr[t], v[t]])
+
+
+def _window_attention(q, gate, cache, slot, block_table, st, out, heads, kv_heads, dk, dv, rot_dims, window, scale, sink, cos, sin):
+    T = q.shape[0]
+    qa = _rot_pairs(q.float().view(T, heads, dk), cos, sin, rot_dims) * scale
+    rep = heads // kv_heads
+    for t, (sq, p) in enumerate(zip(st.token_seq_ids.tolist(), st.token_positions.tolist())):
+        lo = max(0, p - window + 1) if window > 0 else 0
+        rows = _cache_rows(cache, slot, block_table, sq, list(range(lo, p + 1))).float()      # [n, G (dk + dv)]
+        ks = rows[:, :kv_heads * dk].view(-1, kv_heads, dk).repeat_interleave(rep, dim=1)     # [n, H, dk]
+        vs = rows[:, kv_heads * dk:].view(-1, kv_heads, dv).repeat_interleave(rep, dim=1)
+        sc = torch.einsum("hd,nhd->hn", qa[t], ks)
+        if sink:
+            sc = torch.cat([sc, torch.zeros(heads, 1)], dim=1)
+        pr = torch.softmax(sc, dim=-1)[:, :rows.shape[0]]
+        o = torch.einsum("hn,nhd->hd", pr, vs).reshape(heads * dv)
+        if gate is not None:
+            o = o * torch.sigmoid(gate[t].float())
+        out[t] = o.to(out.dtype)
+
+
 class GlooFusedAllReduce:
     """CPU stand-in of swiftllm_b200.worker.tp_comm.FusedAllReduce with the SAME observable semantics as the CUDA kernels
     (csrc/allreduce_norm.cu), exchanged over gloo: partials are summed in rank order in fp32, residual <- h(h(sum) + residual),
@@ -266,7 +320,11 @@ _PATCHES = [
     ("swiftllm_b200.worker.block_manager", "gather_allocated_blocks_and_unset", _gather_and_unset),
     ("swiftllm_b200.swiftllm_c", "swap_blocks", _swap_blocks),
     ("swiftllm_b200.swiftllm_c", "swap_blocks_device", _swap_blocks_device),
-    ("swiftllm_b200.worker.bupozen_model", "add_rmsnorm_f32", _add_rmsnorm_f32),
+    ("swiftllm_b200.worker.parallel_block_model", "add_rmsnorm_f32", _add_rmsnorm_f32),
+    ("swiftllm_b200.worker.layers.window_attention", "window_kv_store", _window_kv_store),
+    ("swiftllm_b200.worker.layers.window_attention", "window_attention", _window_attention),
+    ("swiftllm_b200.worker.layers.feed_forward", "moe_route_grouped", _moe_route_grouped),
+    ("swiftllm_b200.worker.layers.feed_forward", "moe_clamped_glu_scale", _moe_clamped_glu_scale),
     ("swiftllm_b200.worker.layers.latent_attention", "rmsnorm_strided", _rmsnorm_strided),
     ("swiftllm_b200.worker.layers.latent_attention", "latent_kv_store", _latent_kv_store),
     ("swiftllm_b200.worker.layers.latent_attention", "latent_attention", _latent_attention),
