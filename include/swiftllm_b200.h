@@ -285,12 +285,18 @@ int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int
  *   out[i, h, :dv] = sigmoid(gate[i, h, :dv]) * sum_j p_j v_j,   p_j = exp(s_j) / (sink + sum_j' exp(s_j')),
  *   s_j = rotary(q[i, h]) . k_j * scale;  sink = 1: the softmax has a value-less sink of score 0 (one more in the denominator).
  * q [T, num_heads * dk] un-rotated, gate [T, num_heads * dv] logits or NULL, out [T, num_heads * dv]; row strides in elements.
- * dv <= 256. */
+ * dv <= 256.  Rows [0, num_prefill_tokens) of the step are prompt portions, the others single decoded tokens (a hint for how
+ * tokens are grouped into CTAs; any value in 0 .. num_tokens gives the same result).
+ * 16-bit dtypes with dk, dv multiples of 16 and <= 128 run on tensor cores (mma.sync over tokens x heads of a key/value group);
+ * other shapes and SLLM_F32 run the fp32 CUDA-core kernel.  sllm_window_attention_set_simt(1) forces the latter (returns the
+ * old setting). */
+int sllm_window_attention_set_simt(int on);
 int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, const void* sinb, const void* gate,
                           int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
-                          int64_t out_stride_t, int64_t num_tokens, int num_heads, int num_kv_heads, int dk, int dv,
-                          int rot_dims, int window, float scale, int sink, sllm_dtype_t dtype, sllm_stream_t stream);
+                          int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill_tokens, int num_heads, int num_kv_heads,
+                          int dk, int dv, int rot_dims, int window, float scale, int sink, sllm_dtype_t dtype,
+                          sllm_stream_t stream);
 
 #ifdef __cplusplus
 }

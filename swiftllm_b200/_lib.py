@@ -56,8 +56,9 @@ SIGNATURES = {
     "sllm_latent_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I,
                                    _I, _I, _I, _F, _I, _P, _I, _P]),
     "sllm_window_kv_store": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _L, _I, _I, _I, _I, _I, _P]),
-    "sllm_window_attention": (_I, [_P, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _I, _F,
-                                   _I, _I, _P]),
+    "sllm_window_attention_set_simt": (_I, [_I]),
+    "sllm_window_attention": (_I, [_P, _L, _P, _P, _P, _L, _P, _I, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _I,
+                                   _F, _I, _I, _P]),
 }
 
 _lib = None

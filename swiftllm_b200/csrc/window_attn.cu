@@ -8,6 +8,7 @@
 // position p sees the positions max(0, p - window + 1) .. p (window <= 0: all of 0 .. p).  Rotary pairs are interleaved
 // ((2i, 2i+1), the first rot_dims entries of a head; the rest pass through).  Softmax, rotation and the weighted sum of values
 // run in fp32 for every storage type.
+#include "mma_helpers.cuh"
 #include "typed_io.cuh"
 
 namespace sllm {
@@ -148,6 +149,243 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
     }
 }
 
+
+// ------------------------------------------------------------------ attention (tensor cores, 16-bit storage)
+// One CTA = up to 64 query ROWS of one key/value group: row r is (token r / hqp of the CTA's token range, head r % hqp of the
+// group), hqp = heads per group rounded up to a power of two.  The CTA walks its tokens in SEGMENTS (runs of one sequence at
+// consecutive positions - a prompt portion; a decoded token is a segment of one), and a segment's rows share every staged key
+// tile: 64 keys x (dk + dv), gathered through the block table with cp.async into a two-stage ring while the previous tile is
+// multiplied.  Warp w owns rows 16 w .. 16 w + 15: S = Q K^T (mma.sync m16n8k16, fp32 accumulate), per-row window mask, online
+// softmax in fp32 (base 2, the sink enters as a key of score 0), P rounded to the storage type and fed from registers into
+// O += P V.  dk, dv multiples of 16, at most DMAX.  Rows of 16-bit tiles are padded by 16 bytes: the eight rows an ldmatrix
+// reads then fall into eight different bank groups for every dk / dv.
+constexpr int WT_KEYS = 64;
+constexpr int WT_ROWS = 64;
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(128) window_attn_mma_kernel(
+    const T* __restrict__ q, int64_t q_stride_t, const float* __restrict__ cosb, const float* __restrict__ sinb,
+    const T* __restrict__ gate, int64_t gate_stride_t, const T* __restrict__ cache, int n_slots, int slot, int block_size,
+    const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
+    const int* __restrict__ tok_pos, T* __restrict__ out, int64_t out_stride_t, int row0, int nrows, int qt, int hq, int hqp_log2,
+    int H, int G, int dk, int dv, int rot_dims, int window, float scale_log2, float sink) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int PQ = dk * 2 + 16, PK = dk * 2 + 16, PV = dv * 2 + 16;            // row pitches in bytes
+    unsigned char* Qs = smem_raw;                                              // [64][PQ]
+    unsigned char* Ks = Qs + WT_ROWS * PQ;                                     // [2][64][PK]
+    unsigned char* Vs = Ks + 2 * WT_KEYS * PK;                                 // [2][64][PV]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = blockIdx.y;
+    const int hqp = 1 << hqp_log2;
+    const int t_first = row0 + blockIdx.x * qt;
+    const int ntok = min(qt, row0 + nrows - t_first);
+    const int row_elems = G * (dk + dv);
+    const int ck = dk >> 3, cv = dv >> 3;                                      // 16-byte chunks per key / value row
+    const int half = rot_dims >> 1;
+
+    for (int i0 = 0; i0 < ntok;) {
+        // ---- the segment: tokens t_first + i0 .. + n - 1 of one sequence at consecutive positions
+        const int ts = t_first + i0;
+        const int seq = tok_seq[ts], pos0 = tok_pos[ts];
+        int n = 1;
+        while (i0 + n < ntok && tok_seq[ts + n] == seq && tok_pos[ts + n] == pos0 + n) n++;
+        const int* bt = block_table + (int64_t)seq * max_blocks_per_seq;
+        const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+        const int hi = pos0 + n - 1;
+        const int ntiles = (hi - lo) / WT_KEYS + 1;
+        __syncthreads();                                                       // the previous segment's tiles and queries are done with
+
+        auto load_tile = [&](int it) {
+            const int base = lo + it * WT_KEYS, st = it & 1;
+            for (int c = tid; c < WT_KEYS * (ck + cv); c += 128) {
+                const bool is_v = c >= WT_KEYS * ck;
+                const int cc = is_v ? c - WT_KEYS * ck : c;
+                const int per = is_v ? cv : ck;
+                const int jj = cc / per, ch = cc - jj * per;
+                const int kp = base + jj;
+                const bool ok = kp <= hi;
+                const T* src = cache;
+                if (ok) {
+                    const int64_t rowi = ((int64_t)bt[kp / block_size] * n_slots + slot) * block_size + kp % block_size;
+                    src = cache + rowi * row_elems + (is_v ? G * dk + g * dv : g * dk) + ch * 8;
+                }
+                unsigned char* dst = is_v ? Vs + (st * WT_KEYS + jj) * PV + ch * 16 : Ks + (st * WT_KEYS + jj) * PK + ch * 16;
+                cp_async16(smem_u32(dst), src, ok ? 16 : 0);
+            }
+            cp_async_commit();
+        };
+        load_tile(0);
+
+        // ---- queries of the segment: rotated in fp32, rounded to the storage type; dead rows are zeros
+        for (int c = tid; c < WT_ROWS * (dk >> 1); c += 128) {
+            const int r = c / (dk >> 1), i = c - r * (dk >> 1);
+            const int j = r >> hqp_log2, hh = r & (hqp - 1);
+            float a = 0.f, b = 0.f;
+            if (j < n && hh < hq) {
+                const int64_t t = ts + j;
+                const T* qr = q + t * q_stride_t + (int64_t)(g * hq + hh) * dk;
+                a = ldf(qr + 2 * i); b = ldf(qr + 2 * i + 1);
+                if (2 * i < rot_dims) {
+                    const float cs = cosb[t * half + i], sn = sinb[t * half + i];
+                    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+                    a = ra; b = rb;
+                }
+            }
+            *reinterpret_cast<uint32_t*>(Qs + r * PQ + i * 4) = pack2<T>(a, b);
+        }
+
+        // ---- per-thread state: rows (lane / 4) and (lane / 4) + 8 of the warp's 16
+        const int r_a = warp * 16 + (lane >> 2), r_b = r_a + 8;
+        const int j_a = r_a >> hqp_log2, j_b = r_b >> hqp_log2;
+        const bool live_a = j_a < n && (r_a & (hqp - 1)) < hq, live_b = j_b < n && (r_b & (hqp - 1)) < hq;
+        const int pos_a = pos0 + j_a, pos_b = pos0 + j_b;
+        const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+        // keys any row of this warp can see (warp-uniform): tiles outside are skipped
+        const int wj_min = (warp * 16) >> hqp_log2, wj_max = min((warp * 16 + 15) >> hqp_log2, n - 1);
+        const bool warp_live = wj_min < n;
+        const int w_lo = window > 0 ? max(0, pos0 + wj_min - window + 1) : 0, w_hi = pos0 + wj_max;
+        float m_a = sink > 0.f ? 0.f : -INFINITY, m_b = m_a;
+        float l_a = (lane & 3) == 0 ? sink : 0.f, l_b = l_a;
+        float o[DMAX / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < DMAX / 8; nt++) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+
+        for (int it = 0; it < ntiles; it++) {
+            if (it + 1 < ntiles) { load_tile(it + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+            __syncthreads();                                                   // tile `it` (and, first time, the queries) visible
+            const int base = lo + it * WT_KEYS;
+            if (warp_live && base <= w_hi && base + WT_KEYS - 1 >= w_lo) {
+                const unsigned char* Kt = Ks + (it & 1) * WT_KEYS * PK;
+                const unsigned char* Vt = Vs + (it & 1) * WT_KEYS * PV;
+                float sc[8][4];
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+                for (int kk = 0; kk < DMAX / 16; kk++) {
+                    if (kk * 16 < dk) {
+                        uint32_t a[4];
+                        ldmatrix_x4(smem_u32(Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PQ + (kk * 16 + (lane >> 4) * 8) * 2),
+                                    a[0], a[1], a[2], a[3]);
+#pragma unroll
+                        for (int np = 0; np < 4; np++) {
+                            uint32_t b0, b1, b2, b3;
+                            ldmatrix_x4(smem_u32(Kt + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * PK + (kk * 16 + ((lane >> 3) & 1) * 8) * 2),
+                                        b0, b1, b2, b3);
+                            mma_16816<T>(sc[2 * np], a, b0, b1);
+                            mma_16816<T>(sc[2 * np + 1], a, b2, b3);
+                        }
+                    }
+                }
+                // mask, running maximum
+                float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int kp = base + nt * 8 + (lane & 3) * 2 + e;
+                        const bool va = live_a && kp <= pos_a && kp >= lo_a, vb = live_b && kp <= pos_b && kp >= lo_b;
+                        sc[nt][e] = va ? sc[nt][e] * scale_log2 : -INFINITY;
+                        sc[nt][2 + e] = vb ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+                        mx_a = fmaxf(mx_a, sc[nt][e]);
+                        mx_b = fmaxf(mx_b, sc[nt][2 + e]);
+                    }
+                }
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+                const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+                const float ref_a = mn_a == -INFINITY ? 0.f : mn_a, ref_b = mn_b == -INFINITY ? 0.f : mn_b;   // nothing seen yet
+                const float al_a = exp2f(m_a - ref_a), al_b = exp2f(m_b - ref_b);                             // exp2(-inf) = 0
+                m_a = mn_a; m_b = mn_b;
+                l_a *= al_a; l_b *= al_b;
+#pragma unroll
+                for (int nt = 0; nt < DMAX / 8; nt++) { o[nt][0] *= al_a; o[nt][1] *= al_a; o[nt][2] *= al_b; o[nt][3] *= al_b; }
+                uint32_t pa[4][4];
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++) {
+                    const float p0 = exp2f(sc[nt][0] - ref_a), p1 = exp2f(sc[nt][1] - ref_a);
+                    const float p2 = exp2f(sc[nt][2] - ref_b), p3 = exp2f(sc[nt][3] - ref_b);
+                    l_a += p0 + p1; l_b += p2 + p3;
+                    pa[nt >> 1][(nt & 1) * 2] = pack2<T>(p0, p1);
+                    pa[nt >> 1][(nt & 1) * 2 + 1] = pack2<T>(p2, p3);
+                }
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {                               // 16 keys per step
+#pragma unroll
+                    for (int np = 0; np < DMAX / 16; np++) {
+                        if (np * 16 < dv) {
+                            uint32_t b0, b1, b2, b3;
+                            ldmatrix_x4_trans(smem_u32(Vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PV + (np * 16 + (lane >> 4) * 8) * 2),
+                                              b0, b1, b2, b3);
+                            mma_16816<T>(o[2 * np], pa[kk], b0, b1);
+                            mma_16816<T>(o[2 * np + 1], pa[kk], b2, b3);
+                        }
+                    }
+                }
+            }
+            __syncthreads();                                                   // stage it & 1 may be overwritten by tile it + 2
+        }
+
+        // ---- normalise, gate, store
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const bool live = e ? live_b : live_a;
+            if (!live) continue;
+            const int r = e ? r_b : r_a;
+            const int64_t t = ts + (r >> hqp_log2);
+            const int h = g * hq + (r & (hqp - 1));
+            const float inv = 1.f / (e ? l_b : l_a);
+            T* orow = out + t * out_stride_t + (int64_t)h * dv;
+            const T* grow = gate != nullptr ? gate + t * gate_stride_t + (int64_t)h * dv : nullptr;
+#pragma unroll
+            for (int nt = 0; nt < DMAX / 8; nt++) {
+                const int d = nt * 8 + (lane & 3) * 2;
+                if (d < dv) {
+                    float y0 = o[nt][2 * e] * inv, y1 = o[nt][2 * e + 1] * inv;
+                    if (grow != nullptr) {
+                        y0 *= 1.f / (1.f + __expf(-ldf(grow + d)));
+                        y1 *= 1.f / (1.f + __expf(-ldf(grow + d + 1)));
+                    }
+                    *reinterpret_cast<uint32_t*>(orow + d) = pack2<T>(y0, y1);
+                }
+            }
+        }
+        i0 += n;
+    }
+}
+
+static bool g_window_simt = false;
+
+// rows [0, num_prefill) are prompt portions (many consecutive tokens of a sequence share a CTA), the rest single decoded tokens
+template <typename T, int DMAX>
+static int launch_window_attn_mma(const void* q, int64_t q_stride_t, const void* cosb, const void* sinb, const void* gate,
+                                  int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
+                                  const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos,
+                                  void* out, int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill, int H, int G, int dk,
+                                  int dv, int rot_dims, int window, float scale, float sink, cudaStream_t stream) {
+    static unsigned long long attr_mask = 0;
+    const int hq = H / G;
+    int hqp_log2 = 0;
+    while ((1 << hqp_log2) < hq) hqp_log2++;
+    const size_t smem = (size_t)WT_ROWS * (dk * 2 + 16) + 2 * (size_t)WT_KEYS * ((dk * 2 + 16) + (dv * 2 + 16));
+    auto kern = window_attn_mma_kernel<T, DMAX>;
+    if (first_use_on_this_device(attr_mask))
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const int64_t parts[2][2] = {{0, num_prefill}, {num_prefill, num_tokens - num_prefill}};
+    for (int k = 0; k < 2; k++) {
+        const int64_t first = parts[k][0], count = parts[k][1];
+        if (count <= 0) continue;
+        const int qt = k == 0 ? WT_ROWS >> hqp_log2 : 1;
+        kern<<<dim3((unsigned)cdiv(count, qt), (unsigned)G), 128, smem, stream>>>(
+            (const T*)q, q_stride_t, (const float*)cosb, (const float*)sinb, (const T*)gate, gate_stride_t, (const T*)cache,
+            n_slots, slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq, (const int*)tok_pos,
+            (T*)out, out_stride_t, (int)first, (int)count, qt, hq, hqp_log2, H, G, dk, dv, rot_dims, window, scale_log2, sink);
+    }
+    return check_launch("window_attention (tensor cores)");
+}
+
 static int heads_per_cta(int hq) {
     for (int n = WA_MAX_HPB; n > 1; n--)
         if (hq % n == 0) return n;
@@ -197,11 +435,18 @@ int sllm_window_kv_store(const void* k, int64_t k_row_stride, const void* v, int
     return check_launch("window_kv_store");
 }
 
+int sllm_window_attention_set_simt(int on) {
+    const int old = g_window_simt ? 1 : 0;
+    g_window_simt = on != 0;
+    return old;
+}
+
 int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, const void* sinb, const void* gate,
                           int64_t gate_stride_t, const void* cache, int n_slots, int slot, int block_size,
                           const void* block_table, int max_blocks_per_seq, const void* tok_seq, const void* tok_pos, void* out,
-                          int64_t out_stride_t, int64_t num_tokens, int num_heads, int num_kv_heads, int dk, int dv,
-                          int rot_dims, int window, float scale, int sink, sllm_dtype_t dtype, sllm_stream_t stream) {
+                          int64_t out_stride_t, int64_t num_tokens, int64_t num_prefill_tokens, int num_heads, int num_kv_heads,
+                          int dk, int dv, int rot_dims, int window, float scale, int sink, sllm_dtype_t dtype,
+                          sllm_stream_t stream) {
     SLLM_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 &&
                  dv <= 256 && rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0,
                  "window_attention: bad shape (heads %d / %d, dk %d, dv %d <= 256, rot_dims %d)", num_heads, num_kv_heads, dk,
@@ -210,7 +455,19 @@ int sllm_window_attention(const void* q, int64_t q_stride_t, const void* cosb, c
     if (num_tokens == 0) return 0;
     SLLM_REQUIRE(q && tok_seq && tok_pos && block_table && cache && out && (rot_dims == 0 || (cosb && sinb)),
                  "window_attention: null pointer");
+    SLLM_REQUIRE(num_prefill_tokens >= 0 && num_prefill_tokens <= num_tokens, "window_attention: bad number of prompt rows");
     const float sinkw = sink ? 1.f : 0.f;
+    const int hq = num_heads / num_kv_heads;
+    if (!g_window_simt && dtype != SLLM_F32 && dk % 16 == 0 && dv % 16 == 0 && dk <= 128 && dv <= 128 && hq <= WT_ROWS &&
+        num_tokens < (1ll << 31)) {
+#define WA_MMA(DMAX)                                                                                                        \
+    SLLM_DISPATCH_DTYPE(dtype, return (launch_window_attn_mma<T, DMAX>(q, q_stride_t, cosb, sinb, gate, gate_stride_t, cache,  \
+        n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out, out_stride_t, num_tokens,         \
+        num_prefill_tokens, num_heads, num_kv_heads, dk, dv, rot_dims, window, scale, sinkw, (cudaStream_t)stream)))
+        if (dk <= 64 && dv <= 64) { WA_MMA(64); }
+        else { WA_MMA(128); }
+#undef WA_MMA
+    }
 #define WA_LAUNCH(KR)                                                                                                      \
     SLLM_DISPATCH_DTYPE_F32(dtype, return (launch_window_attn<T, KR>(q, q_stride_t, cosb, sinb, gate, gate_stride_t, cache,   \
         n_slots, slot, block_size, block_table, max_blocks_per_seq, tok_seq, tok_pos, out, out_stride_t, num_tokens,        \

@@ -34,6 +34,11 @@ def window_attention(q: torch.Tensor, gate, cache: torch.Tensor, slot: int, bloc
     _lib.check(_lib.lib().sllm_window_attention(
         q.data_ptr(), _stride0(q), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(gate), _stride0(gate) if gate is not None else 0,
         cache.data_ptr(), cache.shape[1], slot, cache.shape[2], block_table.data_ptr(), block_table.shape[1],
-        infer_state.token_seq_ids.data_ptr(), infer_state.token_positions.data_ptr(), out.data_ptr(), _stride0(out), T, heads,
-        kv_heads, dk, dv, rot_dims, window, scale, 1 if sink else 0, _lib.dtype_tag_f32(q.dtype), _lib.stream()),
+        infer_state.token_seq_ids.data_ptr(), infer_state.token_positions.data_ptr(), out.data_ptr(), _stride0(out), T,
+        min(T, max(0, int(getattr(infer_state, "num_prefill_tokens", T)))), heads, kv_heads, dk, dv, rot_dims, window, scale, 1 if sink else 0, _lib.dtype_tag_f32(q.dtype), _lib.stream()),
         "window_attention")
+
+
+def set_simt(on: bool) -> bool:
+    """Force the fp32 CUDA-core attention kernel for every shape (tests compare the two paths); returns the old setting."""
+    return bool(_lib.lib().sllm_window_attention_set_simt(1 if on else 0))

@@ -283,3 +283,46 @@ def test_trace_replay_command_line(tmp_path):
             for j, (k, pos) in enumerate(rr):
                 err = np.sqrt(((got[j] - ref[k][pos]) ** 2).mean() / (ref[k][pos] ** 2).mean())
                 assert err < limit, (dtype, n, k, pos, err)
+
+
+@pytest.mark.parametrize("H,G,dk,dv,window", [(8, 1, 64, 32, 96), (6, 2, 32, 16, 40), (16, 1, 16, 16, 7), (4, 4, 128, 128, 0),
+                                              (12, 4, 48, 80, 150), (64, 1, 16, 32, 33)])
+def test_tensor_core_and_cuda_core_attention_agree(H, G, dk, dv, window):
+    """The same mixed step (two prompt portions that start inside a sequence, a one-token prompt, three decoded tokens) through
+    the tensor-core kernel and through the fp32 CUDA-core kernel: bf16 storage, heads per group that are not a power of two,
+    several key tiles, token runs that end inside a CTA's token range."""
+    from swiftllm_b200.worker.kernels import window_attn as WA
+    g = torch.Generator().manual_seed(H + dk)
+    bs, lens = 16, [300, 77, 1, 200, 130, 65]                 # cached lengths after this step
+    new = [150, 40, 1, 1, 1, 1]                              # tokens of this step per sequence (the last ones)
+    nb = sum((n + bs - 1) // bs for n in lens)
+    perm = torch.randperm(nb, generator=g).tolist()
+    table = torch.full((6, 32), -1, dtype=torch.int32)
+    for s, n in enumerate(lens):
+        for b in range((n + bs - 1) // bs):
+            table[s, b] = perm.pop()
+    cache = (torch.randn(nb, 1, bs, G * (dk + dv), generator=g)).to(torch.bfloat16).to(DEV)
+    tok_seq = [s for s, n in enumerate(new) for _ in range(n)]
+    tok_pos = [lens[s] - n + p for s, n in enumerate(new) for p in range(n)]
+    T = len(tok_seq)
+    q = torch.randn(T, H * dk, generator=g).to(torch.bfloat16).to(DEV)
+    gate = torch.randn(T, H * dv, generator=g).to(torch.bfloat16).to(DEV)
+    dims = dk // 2
+    ang = torch.tensor(tok_pos, dtype=torch.float64)[:, None] * torch.tensor([100.0 ** (-2.0 * i / dims) for i in range(dims // 2)],
+                                                                             dtype=torch.float64)[None]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    st = types.SimpleNamespace(token_seq_ids=torch.tensor(tok_seq, dtype=torch.int32, device=DEV),
+                               token_positions=torch.tensor(tok_pos, dtype=torch.int32, device=DEV), num_prefill_tokens=191)
+    outs = []
+    for simt in (True, False):
+        old = WA.set_simt(simt)
+        try:
+            out = torch.zeros(T, H * dv, dtype=torch.bfloat16, device=DEV)
+            WA.window_attention(q, gate, cache, 0, table.to(DEV), st, out, H, G, dk, dv, dims, window, dk ** -0.5, True, cos, sin)
+            outs.append(out.float().cpu())
+        finally:
+            WA.set_simt(old)
+    assert B.rel_err(outs[1], outs[0]) < 1.5e-2
+    # every row on its own is close too (a row that saw a wrong window would stand out)
+    row_err = (outs[1] - outs[0]).pow(2).mean(-1).sqrt() / outs[0].pow(2).mean(-1).sqrt()
+    assert float(row_err.max()) < 4e-2
