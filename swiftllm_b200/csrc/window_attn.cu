@@ -195,43 +195,45 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
         const int ntiles = (hi - lo) / WT_KEYS + 1;
         __syncthreads();                                                       // the previous segment's tiles and queries are done with
 
+        // two threads per key row, alternating 16-byte chunks: ONE block-table lookup and address per thread and tile
         auto load_tile = [&](int it) {
-            const int base = lo + it * WT_KEYS, st = it & 1;
-            for (int c = tid; c < WT_KEYS * (ck + cv); c += 128) {
-                const bool is_v = c >= WT_KEYS * ck;
-                const int cc = is_v ? c - WT_KEYS * ck : c;
-                const int per = is_v ? cv : ck;
-                const int jj = cc / per, ch = cc - jj * per;
-                const int kp = base + jj;
-                const bool ok = kp <= hi;
-                const T* src = cache;
-                if (ok) {
-                    const int64_t rowi = ((int64_t)bt[kp / block_size] * n_slots + slot) * block_size + kp % block_size;
-                    src = cache + rowi * row_elems + (is_v ? G * dk + g * dv : g * dk) + ch * 8;
-                }
-                unsigned char* dst = is_v ? Vs + (st * WT_KEYS + jj) * PV + ch * 16 : Ks + (st * WT_KEYS + jj) * PK + ch * 16;
-                cp_async16(smem_u32(dst), src, ok ? 16 : 0);
+            const int st = it & 1, jj = tid >> 1, part = tid & 1;
+            const int kp = lo + it * WT_KEYS + jj;
+            const bool ok = kp <= hi;
+            const T* krow = cache;
+            const T* vrow = cache;
+            if (ok) {
+                const int b = kp / block_size;
+                const int64_t rowi = ((int64_t)bt[b] * n_slots + slot) * block_size + (kp - b * block_size);
+                krow = cache + rowi * row_elems + g * dk;
+                vrow = cache + rowi * row_elems + G * dk + g * dv;
             }
+            const int nb = ok ? 16 : 0;
+            const uint32_t kd = smem_u32(Ks + (st * WT_KEYS + jj) * PK), vd = smem_u32(Vs + (st * WT_KEYS + jj) * PV);
+            for (int ch = part; ch < ck; ch += 2) cp_async16(kd + ch * 16, ok ? krow + ch * 8 : krow, nb);
+            for (int ch = part; ch < cv; ch += 2) cp_async16(vd + ch * 16, ok ? vrow + ch * 8 : vrow, nb);
             cp_async_commit();
         };
         load_tile(0);
 
         // ---- queries of the segment: rotated in fp32, rounded to the storage type; dead rows are zeros
-        for (int c = tid; c < WT_ROWS * (dk >> 1); c += 128) {
-            const int r = c / (dk >> 1), i = c - r * (dk >> 1);
+        for (int r = tid >> 1; r < WT_ROWS; r += 64) {                         // two threads per row
             const int j = r >> hqp_log2, hh = r & (hqp - 1);
-            float a = 0.f, b = 0.f;
-            if (j < n && hh < hq) {
-                const int64_t t = ts + j;
-                const T* qr = q + t * q_stride_t + (int64_t)(g * hq + hh) * dk;
-                a = ldf(qr + 2 * i); b = ldf(qr + 2 * i + 1);
-                if (2 * i < rot_dims) {
-                    const float cs = cosb[t * half + i], sn = sinb[t * half + i];
-                    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
-                    a = ra; b = rb;
+            const bool live = j < n && hh < hq;
+            const int64_t t = ts + j;
+            const T* qr = q + t * q_stride_t + (int64_t)(g * hq + hh) * dk;
+            for (int i = tid & 1; i < (dk >> 1); i += 2) {
+                float a = 0.f, b = 0.f;
+                if (live) {
+                    a = ldf(qr + 2 * i); b = ldf(qr + 2 * i + 1);
+                    if (2 * i < rot_dims) {
+                        const float cs = cosb[t * half + i], sn = sinb[t * half + i];
+                        const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+                        a = ra; b = rb;
+                    }
                 }
+                *reinterpret_cast<uint32_t*>(Qs + r * PQ + i * 4) = pack2<T>(a, b);
             }
-            *reinterpret_cast<uint32_t*>(Qs + r * PQ + i * 4) = pack2<T>(a, b);
         }
 
         // ---- per-thread state: rows (lane / 4) and (lane / 4) + 8 of the warp's 16
