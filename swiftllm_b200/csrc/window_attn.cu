@@ -8,6 +8,8 @@
 // position p sees the positions max(0, p - window + 1) .. p (window <= 0: all of 0 .. p).  Rotary pairs are interleaved
 // ((2i, 2i+1), the first rot_dims entries of a head; the rest pass through).  Softmax, rotation and the weighted sum of values
 // run in fp32 for every storage type.
+#include <stdlib.h>
+
 #include "mma_helpers.cuh"
 #include "typed_io.cuh"
 
@@ -159,11 +161,12 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
 // softmax in fp32 (base 2, the sink enters as a key of score 0), P rounded to the storage type and fed from registers into
 // O += P V.  dk, dv multiples of 16, at most DMAX.  Rows of 16-bit tiles are padded by 16 bytes: the eight rows an ldmatrix
 // reads then fall into eight different bank groups for every dk / dv.
-constexpr int WT_KEYS = 64;
 constexpr int WT_ROWS = 64;
 
-template <typename T, int DMAX>
-__global__ void __launch_bounds__(128) window_attn_mma_kernel(
+// WT_KEYS: keys per tile (32 or 64).  Smaller tiles leave room for more CTAs per SM (prompt portions: many CTAs, latency-bound);
+// larger ones keep more bytes in flight per CTA (decoded tokens: few CTAs that walk their window alone).
+template <typename T, int DMAX, int WT_KEYS>
+__global__ void __launch_bounds__(128, WT_KEYS == 32 ? 3 : 2) window_attn_mma_kernel(
     const T* __restrict__ q, int64_t q_stride_t, const float* __restrict__ cosb, const float* __restrict__ sinb,
     const T* __restrict__ gate, int64_t gate_stride_t, const T* __restrict__ cache, int n_slots, int slot, int block_size,
     const int* __restrict__ block_table, int max_blocks_per_seq, const int* __restrict__ tok_seq,
@@ -197,7 +200,8 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
 
         // two threads per key row, alternating 16-byte chunks: ONE block-table lookup and address per thread and tile
         auto load_tile = [&](int it) {
-            const int st = it & 1, jj = tid >> 1, part = tid & 1;
+            constexpr int TPR = 128 / WT_KEYS;                                 // threads per key row
+            const int st = it & 1, jj = tid / TPR, part = tid % TPR;
             const int kp = lo + it * WT_KEYS + jj;
             const bool ok = kp <= hi;
             const T* krow = cache;
@@ -210,8 +214,8 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
             }
             const int nb = ok ? 16 : 0;
             const uint32_t kd = smem_u32(Ks + (st * WT_KEYS + jj) * PK), vd = smem_u32(Vs + (st * WT_KEYS + jj) * PV);
-            for (int ch = part; ch < ck; ch += 2) cp_async16(kd + ch * 16, ok ? krow + ch * 8 : krow, nb);
-            for (int ch = part; ch < cv; ch += 2) cp_async16(vd + ch * 16, ok ? vrow + ch * 8 : vrow, nb);
+            for (int ch = part; ch < ck; ch += TPR) cp_async16(kd + ch * 16, ok ? krow + ch * 8 : krow, nb);
+            for (int ch = part; ch < cv; ch += TPR) cp_async16(vd + ch * 16, ok ? vrow + ch * 8 : vrow, nb);
             cp_async_commit();
         };
         load_tile(0);
@@ -259,9 +263,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
             if (warp_live && base <= w_hi && base + WT_KEYS - 1 >= w_lo) {
                 const unsigned char* Kt = Ks + (it & 1) * WT_KEYS * PK;
                 const unsigned char* Vt = Vs + (it & 1) * WT_KEYS * PV;
-                float sc[8][4];
+                float sc[WT_KEYS / 8][4];
 #pragma unroll
-                for (int nt = 0; nt < 8; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+                for (int nt = 0; nt < WT_KEYS / 8; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
 #pragma unroll
                 for (int kk = 0; kk < DMAX / 16; kk++) {
                     if (kk * 16 < dk) {
@@ -269,7 +273,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
                         ldmatrix_x4(smem_u32(Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PQ + (kk * 16 + (lane >> 4) * 8) * 2),
                                     a[0], a[1], a[2], a[3]);
 #pragma unroll
-                        for (int np = 0; np < 4; np++) {
+                        for (int np = 0; np < WT_KEYS / 16; np++) {
                             uint32_t b0, b1, b2, b3;
                             ldmatrix_x4(smem_u32(Kt + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * PK + (kk * 16 + ((lane >> 3) & 1) * 8) * 2),
                                         b0, b1, b2, b3);
@@ -281,7 +285,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
                 // mask, running maximum
                 float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-                for (int nt = 0; nt < 8; nt++) {
+                for (int nt = 0; nt < WT_KEYS / 8; nt++) {
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         const int kp = base + nt * 8 + (lane & 3) * 2 + e;
@@ -301,9 +305,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
                 l_a *= al_a; l_b *= al_b;
 #pragma unroll
                 for (int nt = 0; nt < DMAX / 8; nt++) { o[nt][0] *= al_a; o[nt][1] *= al_a; o[nt][2] *= al_b; o[nt][3] *= al_b; }
-                uint32_t pa[4][4];
+                uint32_t pa[WT_KEYS / 16][4];
 #pragma unroll
-                for (int nt = 0; nt < 8; nt++) {
+                for (int nt = 0; nt < WT_KEYS / 8; nt++) {
                     const float p0 = exp2f(sc[nt][0] - ref_a), p1 = exp2f(sc[nt][1] - ref_a);
                     const float p2 = exp2f(sc[nt][2] - ref_b), p3 = exp2f(sc[nt][3] - ref_b);
                     l_a += p0 + p1; l_b += p2 + p3;
@@ -311,7 +315,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
                     pa[nt >> 1][(nt & 1) * 2 + 1] = pack2<T>(p2, p3);
                 }
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++) {                               // 16 keys per step
+                for (int kk = 0; kk < WT_KEYS / 16; kk++) {                    // 16 keys per step
 #pragma unroll
                     for (int np = 0; np < DMAX / 16; np++) {
                         if (np * 16 < dv) {
@@ -370,17 +374,23 @@ static int launch_window_attn_mma(const void* q, int64_t q_stride_t, const void*
     const int hq = H / G;
     int hqp_log2 = 0;
     while ((1 << hqp_log2) < hq) hqp_log2++;
-    const size_t smem = (size_t)WT_ROWS * (dk * 2 + 16) + 2 * (size_t)WT_KEYS * ((dk * 2 + 16) + (dv * 2 + 16));
-    auto kern = window_attn_mma_kernel<T, DMAX>;
-    if (first_use_on_this_device(attr_mask))
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+    auto kern_prompt = window_attn_mma_kernel<T, DMAX, 32>;
+    auto kern_decode = window_attn_mma_kernel<T, DMAX, 64>;
+    if (first_use_on_this_device(attr_mask)) {
+        cudaFuncSetAttribute(kern_prompt, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+        cudaFuncSetAttribute(kern_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+    }
+    static const int kt_prompt = getenv("SLLM_WA_KT_PROMPT") ? atoi(getenv("SLLM_WA_KT_PROMPT")) : 32;
+    static const int kt_decode = getenv("SLLM_WA_KT_DECODE") ? atoi(getenv("SLLM_WA_KT_DECODE")) : 64;
     const float scale_log2 = scale * 1.4426950408889634f;
     const int64_t parts[2][2] = {{0, num_prefill}, {num_prefill, num_tokens - num_prefill}};
     for (int k = 0; k < 2; k++) {
         const int64_t first = parts[k][0], count = parts[k][1];
         if (count <= 0) continue;
         const int qt = k == 0 ? WT_ROWS >> hqp_log2 : 1;
-        kern<<<dim3((unsigned)cdiv(count, qt), (unsigned)G), 128, smem, stream>>>(
+        const int keys = k == 0 ? kt_prompt : kt_decode;
+        const size_t smem = (size_t)WT_ROWS * (dk * 2 + 16) + 2 * (size_t)keys * ((dk * 2 + 16) + (dv * 2 + 16));
+        (keys == 32 ? kern_prompt : kern_decode)<<<dim3((unsigned)cdiv(count, qt), (unsigned)G), 128, smem, stream>>>(
             (const T*)q, q_stride_t, (const float*)cosb, (const float*)sinb, (const T*)gate, gate_stride_t, (const T*)cache,
             n_slots, slot, block_size, (const int*)block_table, max_blocks_per_seq, (const int*)tok_seq, (const int*)tok_pos,
             (T*)out, out_stride_t, (int)first, (int)count, qt, hq, hqp_log2, H, G, dk, dv, rot_dims, window, scale_log2, sink);
