@@ -8,8 +8,6 @@
 // position p sees the positions max(0, p - window + 1) .. p (window <= 0: all of 0 .. p).  Rotary pairs are interleaved
 // ((2i, 2i+1), the first rot_dims entries of a head; the rest pass through).  Softmax, rotation and the weighted sum of values
 // run in fp32 for every storage type.
-#include <stdlib.h>
-
 #include "mma_helpers.cuh"
 #include "typed_io.cuh"
 
@@ -156,8 +154,8 @@ __global__ void __launch_bounds__(WA_MAX_HPB * 32) window_attn_kernel(
 // One CTA = up to 64 query ROWS of one key/value group: row r is (token r / hqp of the CTA's token range, head r % hqp of the
 // group), hqp = heads per group rounded up to a power of two.  The CTA walks its tokens in SEGMENTS (runs of one sequence at
 // consecutive positions - a prompt portion; a decoded token is a segment of one), and a segment's rows share every staged key
-// tile: 64 keys x (dk + dv), gathered through the block table with cp.async into a two-stage ring while the previous tile is
-// multiplied.  Warp w owns rows 16 w .. 16 w + 15: S = Q K^T (mma.sync m16n8k16, fp32 accumulate), per-row window mask, online
+// tile: WT_KEYS keys x (dk + dv), gathered through the block table with cp.async into a two-stage ring while the previous tile is
+// multiplied (32-key tiles for prompt portions and large decode batches, see the launcher).  Warp w owns rows 16 w .. 16 w + 15: S = Q K^T (mma.sync m16n8k16, fp32 accumulate), per-row window mask, online
 // softmax in fp32 (base 2, the sink enters as a key of score 0), P rounded to the storage type and fed from registers into
 // O += P V.  dk, dv multiples of 16, at most DMAX.  Rows of 16-bit tiles are padded by 16 bytes: the eight rows an ldmatrix
 // reads then fall into eight different bank groups for every dk / dv.
@@ -380,15 +378,17 @@ static int launch_window_attn_mma(const void* q, int64_t q_stride_t, const void*
         cudaFuncSetAttribute(kern_prompt, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
         cudaFuncSetAttribute(kern_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
     }
-    static const int kt_prompt = getenv("SLLM_WA_KT_PROMPT") ? atoi(getenv("SLLM_WA_KT_PROMPT")) : 32;
-    static const int kt_decode = getenv("SLLM_WA_KT_DECODE") ? atoi(getenv("SLLM_WA_KT_DECODE")) : 64;
+    int num_sms = 0;
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, current_device());
     const float scale_log2 = scale * 1.4426950408889634f;
     const int64_t parts[2][2] = {{0, num_prefill}, {num_prefill, num_tokens - num_prefill}};
     for (int k = 0; k < 2; k++) {
         const int64_t first = parts[k][0], count = parts[k][1];
         if (count <= 0) continue;
         const int qt = k == 0 ? WT_ROWS >> hqp_log2 : 1;
-        const int keys = k == 0 ? kt_prompt : kt_decode;
+        // measured on B200 (128 + 128 per head): prompt portions 24 - 26 % faster with 32-key tiles (three CTAs per SM instead of
+        // two); decoded tokens faster with 64-key tiles at 512 CTAs (357 vs 385 us), with 32-key tiles at 2048 CTAs (950 vs 1220 us)
+        const int keys = (k == 0 || count * G >= 7 * (int64_t)num_sms) ? 32 : 64;
         const size_t smem = (size_t)WT_ROWS * (dk * 2 + 16) + 2 * (size_t)keys * ((dk * 2 + 16) + (dv * 2 + 16));
         (keys == 32 ? kern_prompt : kern_decode)<<<dim3((unsigned)cdiv(count, qt), (unsigned)G), 128, smem, stream>>>(
             (const T*)q, q_stride_t, (const float*)cosb, (const float*)sinb, (const T*)gate, gate_stride_t, (const T*)cache,
